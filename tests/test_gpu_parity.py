@@ -1,0 +1,154 @@
+"""CUDA path against the CPU oracle, through the C ABI, on a B200.
+
+Mirrors the reference's device validation (`benchmarks/attention/run_sparse.py:171-338`):
+the eight named cases at the default policy (B4 / T16 / H64 / D512), ragged explicit query
+lengths, guard bytes behind every buffer, inputs unchanged, the gathered index set compared
+bit for bit, the output compared with the independent FP32 formula.
+"""
+
+import numpy as np
+import pytest
+
+from oracle import sparse_mla_oracle as O
+from tests import support as S
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import torch
+
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from ascendflow_b200 import ops as module
+
+    return module
+
+
+def default_policy(ratio=2, dtype="bf16", b=4, t=16, max_seq=4096):
+    return O.make_policy(b, t, ratio=ratio, max_seq=max_seq, dtype=dtype, blocks=128)
+
+
+def run_case(ops, data, policy, guard=True):
+    import torch
+
+    tensors, buffers = S.to_device(data, policy, guard=guard)
+    before = {name: raw.clone() for name, raw in buffers.items() if name != "attention_out"}
+    ops.sparse_mla(*(tensors[name] for name in S.TENSOR_ORDER))
+    torch.cuda.synchronize()
+    for name, raw in buffers.items():
+        assert bool((raw[-S.GUARD:] == S.GUARD_BYTE).all()), f"{name}: guard bytes changed"
+        if name != "attention_out":
+            assert torch.equal(raw, before[name]), f"{name}: input changed"
+    return tensors, S.output_to_numpy(tensors["attention_out"], policy["DTYPE"])
+
+
+def resolved_on_device(ops, tensors, policy):
+    names = ("cmp_sparse_indices", "ori_block_table", "cmp_block_table", "cu_seqlens_q",
+             "seqused_ori_kv", "seqused_cmp_kv", "cmp_residual_kv", "ori_topk_length")
+    out = ops.resolve_rows(*(tensors[n] for n in names), ori_blocks=policy["ORI_BLOCKS"],
+                           cmp_blocks=policy["CMP_BLOCKS"], cmp_page=policy["PAGE"] // policy["RATIO"])
+    return out.cpu().numpy().astype(np.int64)
+
+
+@pytest.mark.parametrize("case", O.CASES)
+@pytest.mark.parametrize("ratio", [2, 1])
+def test_named_validation_cases(ops, case, ratio):
+    policy = default_policy(ratio)
+    data = O.validation_inputs(policy, case)
+    tensors, actual = run_case(ops, data, policy)
+    assert np.array_equal(resolved_on_device(ops, tensors, policy), O.resolve_rows(data, policy))
+    expected = O.reference_fp32_from_data(data, policy)
+    S.assert_close(actual, expected, f"{case}/C{ratio}")
+    if case == "empty":
+        assert not actual.any()
+
+
+@pytest.mark.parametrize("lens", [[0, 2, 0, 14], [16, 0, 0, 0], [1, 1, 1, 13], [5, 5, 5, 1]])
+def test_explicit_query_lengths(ops, lens):
+    policy = default_policy()
+    data = O.validation_inputs(policy, "mixed", lens)
+    tensors, actual = run_case(ops, data, policy)
+    assert np.array_equal(resolved_on_device(ops, tensors, policy), O.resolve_rows(data, policy))
+    S.assert_close(actual, O.reference_fp32_from_data(data, policy), str(lens))
+
+
+def test_fp16_specialisation(ops):
+    policy = default_policy(dtype="f16")
+    for case in ("mixed", "sink", "replay"):
+        data = O.validation_inputs(policy, case)
+        _, actual = run_case(ops, data, policy)
+        S.assert_close(actual, O.reference_fp32_from_data(data, policy), f"f16/{case}")
+
+
+def test_single_token_and_odd_token_counts(ops):
+    for b, t in ((1, 1), (1, 3), (2, 5), (7, 7)):
+        policy = default_policy(b=b, t=t)
+        policy["ORI_BLOCKS"] = policy["CMP_BLOCKS"] = 64
+        data = O.validation_inputs(policy, "mixed")
+        _, actual = run_case(ops, data, policy)
+        S.assert_close(actual, O.reference_fp32_from_data(data, policy), f"B{b}T{t}")
+
+
+def test_unsorted_indices_and_entries_after_padding(ops):
+    policy = default_policy()
+    data = O.validation_inputs(policy, "mixed")
+    rng = np.random.default_rng(3)
+    for token in range(policy["T"]):
+        row = data["cmp_sparse_indices"][token, 0]
+        live = int((row >= 0).sum())
+        row[:live] = rng.permutation(row[:live])
+        if live + 2 < len(row):
+            row[live + 1] = 0  # after the first -1: must be ignored
+    tensors, actual = run_case(ops, data, policy)
+    assert np.array_equal(resolved_on_device(ops, tensors, policy), O.resolve_rows(data, policy))
+    S.assert_close(actual, O.reference_fp32_from_data(data, policy), "unsorted")
+
+
+def test_future_rows_do_not_leak(ops):
+    """Changing cache rows only a later token may see leaves earlier tokens bit-identical."""
+    import torch
+
+    policy = default_policy(b=1, t=6, max_seq=1024)
+    policy["ORI_BLOCKS"] = policy["CMP_BLOCKS"] = 8
+    arrays, rows, _ = O.performance_inputs(policy, 700, 5)
+    data = dict(arrays, **O.materialize_caches(policy, rows))
+    tensors, first = run_case(ops, data, policy, guard=False)
+    resolved = O.resolve_rows(data, policy)
+    last_only_raw = set(resolved[5, :128].tolist()) - set(resolved[:5, :128].reshape(-1).tolist()) - {-1}
+    assert last_only_raw
+    flat = tensors["ori_kv"].view(-1, 512)
+    flat[torch.as_tensor(sorted(last_only_raw), device=flat.device)] += 4.0
+    ops.sparse_mla(*(tensors[name] for name in S.TENSOR_ORDER))
+    second = S.output_to_numpy(tensors["attention_out"], "bf16")
+    assert np.array_equal(first[:5], second[:5])
+    assert not np.array_equal(first[5], second[5])
+
+
+def test_reference_cpu_configuration(ops):
+    """B=1, 256 queries at the end of a 4096-token context: every token checked."""
+    from ascendflow_b200 import workloads as W
+
+    tensors, meta, work = W.device_case(**W.CONFIGS["cpu_reference_q256_ctx4k"], seed=11)
+    policy = O.make_policy(1, 256, max_seq=4096)
+    ops.sparse_mla(*tensors.values())
+    actual = S.output_to_numpy(tensors["attention_out"], "bf16")
+    tokens = list(range(256))
+    expected = S.sampled_reference(tensors, meta, policy, tokens)
+    S.assert_close(actual, expected, "config 1")
+    assert work["live_rows"] == 163_840 and work["flops"] == 4 * 64 * 512 * 163_840
+
+
+def test_status_block_reports_a_bad_page_without_faulting(ops):
+    import torch
+
+    policy = default_policy()
+    data = O.validation_inputs(policy, "mixed")
+    data["ori_block_table"][1, :] = policy["ORI_BLOCKS"] + 5  # outside the cache: slot masked
+    tensors, _ = S.to_device(data, policy)
+    binding = ops.kernel("sparse_mla")(*(tensors[name] for name in S.TENSOR_ORDER))
+    status = binding.status()
+    assert status[0] == 1
+    actual = S.output_to_numpy(tensors["attention_out"], "bf16")
+    assert np.isfinite(actual).all()
+    torch.cuda.synchronize()
