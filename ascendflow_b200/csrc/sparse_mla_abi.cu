@@ -12,6 +12,7 @@
 #include "../../include/sparse_mla.h"
 #include "sparse_mla_common.cuh"
 #include "sparse_mla_mma_sync.cuh"
+#include "sparse_mla_tcgen05.cuh"
 
 namespace sparse_mla {
 namespace {
@@ -167,13 +168,8 @@ int launch_sparse_mla(void* stream, void* arg_q, void* arg_ori_kv, void* arg_cmp
             B, T, PAGES, ORI_BLOCKS, CMP_BLOCKS, CMP_PAGE))
     return -1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  static bool configured = false;
-  if (int status = configure_once(warp_mma::attention_kernel<__nv_bfloat16>, warp_mma::kSmemBytes, configured))
-    return status;
   if (int status = clear_workspace(s, npu_workspace)) return status;
-  const int grid = int(T < int64_t(multiprocessors()) ? T : multiprocessors());
-  warp_mma::attention_kernel<__nv_bfloat16><<<grid, warp_mma::kThreads, warp_mma::kSmemBytes, s>>>(p);
-  return int(cudaGetLastError());
+  return umma::launch(p, s, multiprocessors());
 }
 
 int launch_sparse_mla_f16(void* stream, void* arg_q, void* arg_ori_kv, void* arg_cmp_kv,
