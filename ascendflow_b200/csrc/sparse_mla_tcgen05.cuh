@@ -1,28 +1,33 @@
-// Sparse MLA attention on the Blackwell tensor path: tcgen05.mma with accumulators in tensor
-// memory, warp-specialised and software-pipelined. BF16 storage, FP32 accumulation and softmax.
+// Sparse MLA attention on the Blackwell tensor path: tcgen05.mma with operands and accumulators
+// in tensor memory, warp-specialised and software-pipelined. BF16 storage, FP32 accumulation.
 //
 // One persistent block per SM owns one query token at a time (64 heads x 512 features) and
 // walks the token's live 64-row chunks (window rows first, then the compressed ranks in list
 // order, as the reference does: examples/sparse_attention/attention.py:42-64, 147-207):
 //
-//   producer warps   resolve slot -> physical row (sparse_mla_common.cuh), then gather the rows
-//                    with 16-byte cp.async into 128-byte-swizzled shared tiles (a row is fetched
-//                    once and serves as K and as V); they also stage the token's Q tile.
-//   MMA warp         one thread issues S = Q X^T (M64 N64 K512, both operands K-major) into a
-//                    double-buffered S tile in tensor memory, and O += P X (M64 N256 x 2 halves,
-//                    X read MN-major from the same tile) into the O accumulator.
-//   softmax warps    tcgen05.ld S, joint online softmax with the per-head sink
-//                    (examples/sparse_attention/attention.py:398-490: one maximum and one
-//                    denominator over window, compressed rows and sink; P rounded to BF16 before
-//                    PV, denominator from unrounded FP32), P to shared memory, O rescaled in
-//                    tensor memory only when the running maximum moved by more than 2^8, final
-//                    normalisation and store.
+//   producer warps   resolve slot -> physical row (sparse_mla_common.cuh) one token ahead, then
+//                    gather the rows with 16-byte cp.async into a three-stage ring of
+//                    128-byte-swizzled shared tiles. A row is fetched once and serves as K and V.
+//   MMA warp         one thread issues S = Q X^T and O += P X. Q and P are read from tensor
+//                    memory, X from the shared tile (K-major for QK, MN-major for PV).
+//   softmax warps    move the token's Q into tensor memory, tcgen05.ld S, joint online softmax
+//                    with the per-head sink (examples/sparse_attention/attention.py:398-490: one
+//                    maximum and one denominator over window, compressed rows and sink; P rounded
+//                    to BF16 before PV, denominator from unrounded FP32), P back to tensor
+//                    memory, O rescaled only when the running maximum moved by more than 2^8,
+//                    final normalisation and store.
 //
-// Tensor memory (512 columns): an M=64 accumulator occupies lanes 0-15 of each 32-lane
-// subpartition; a second one can live in lanes 16-31 of the same columns. O[:, 0:256] and
-// O[:, 256:512] share columns 0-255 that way; S buffers 0 / 1 sit at columns 256 / 320 with
-// lane offsets 0 / 16, so that thread (lane & 15) + 16 * parity of each softmax warp owns one
-// head row of the chunk with that parity.
+// Tensor memory (512 columns x 128 lanes). An M=64 operand or accumulator occupies lanes 0-15 of
+// each 32-lane subpartition; a second one can live in lanes 16-31 of the same columns, and a
+// tcgen05.mma whose A operand comes from tensor memory needs A and D in the same half. The
+// kernel therefore runs two half problems side by side, lane half 0 and lane half 1:
+//   columns   0-255  O[:, 0:256] (half 0)                O[:, 256:512] (half 1)
+//   columns 256-383  Q[:, 0:256] as BF16 pairs (half 0)  Q[:, 256:512] (half 1)
+//   columns 384-511  two S buffers of 64 columns: half 0 holds the partial scores over features
+//                    0-255, half 1 those over 256-511; the softmax threads add the two with
+//                    one shuffle per score. P (BF16 pairs, 32 columns) then overwrites the
+//                    start of the same buffer in both halves and feeds the two PV halves.
+// Thread (lane & 15) + 16 * half of softmax warp w owns head 16 w + (lane & 15) of that half.
 //
 // Every wait on an mbarrier is bounded (tcgen05_ptx.cuh): on expiry the block records
 // kStatusWaitExpired, all roles leave their loops, tensor memory is released, the kernel returns.
@@ -39,31 +44,37 @@ namespace umma {
 using namespace sm100;
 
 constexpr int kSoftmaxWarps = 4;
-constexpr int kProducerWarps = 4;
-constexpr int kMmaWarp = kSoftmaxWarps;                    // warp index 4
-constexpr int kFirstProducerWarp = kSoftmaxWarps + 1;       // warps 5..8
+constexpr int kProducerWarps = 8;
+constexpr int kMmaWarp = kSoftmaxWarps;                     // warp index 4
+constexpr int kFirstProducerWarp = kSoftmaxWarps + 1;
 constexpr int kThreads = 32 * (kSoftmaxWarps + 1 + kProducerWarps);
 constexpr int kProducerThreads = 32 * kProducerWarps;
 
 constexpr int kChunkRows = 64;
 constexpr int kMaxChunks = kSlots / kChunkRows;             // 10
-constexpr int kStages = 2;
+constexpr int kStages = 3;
 constexpr int kBlockBytes = kChunkRows * 128;               // one 64-feature block of a tile: 8 KiB
 constexpr int kTileBytes = 8 * kBlockBytes;                 // 64 rows x 512 features: 64 KiB
 
 // Shared memory map (bytes from a 1024-aligned base).
-constexpr int kSmemQ = 0;
-constexpr int kSmemKv = kSmemQ + kTileBytes;
-constexpr int kSmemP = kSmemKv + kStages * kTileBytes;      // two [64 x 64] BF16 tiles
-constexpr int kSmemRows = kSmemP + 2 * kBlockBytes;         // int[2][640]
+constexpr int kSmemKv = 0;
+constexpr int kSmemRows = kSmemKv + kStages * kTileBytes;   // int[2][640]
 constexpr int kSmemInfo = kSmemRows + 2 * kSlots * 4;       // TokenInfo[2]
 constexpr int kSmemBars = kSmemInfo + 2 * 64;               // mbarriers
 constexpr int kSmemMisc = kSmemBars + 32 * 8;               // tmem slot, abort flag, scratch
+#ifdef SPARSE_MLA_TRACE
+constexpr int kTraceEntries = 2400;
+constexpr int kSmemTrace = kSmemMisc + 64;
+constexpr int kSmemBytes = kSmemTrace + 16 + kTraceEntries * 8 + 1024;
+#else
 constexpr int kSmemBytes = kSmemMisc + 64 + 1024;           // + slack for the 1024-byte alignment
+#endif
 
 constexpr uint32_t kTmemColumns = 512;
 constexpr uint32_t kTmemO = 0;
-constexpr uint32_t kTmemS = 256;                             // buffer b at column 256 + 64 b, lane offset 16 b
+constexpr uint32_t kTmemQ = 256;
+constexpr uint32_t kTmemS = 384;                             // buffer b at column 384 + 64 b
+constexpr uint32_t kHalfLanes = 16u << 16;                   // lane offset of half 1 in a tensor-memory address
 
 struct TokenInfo {
   int token;
@@ -72,8 +83,9 @@ struct TokenInfo {
 };
 
 enum Bar {
-  kQFull0 = 0, kQFull1, kQFree, kKvFull0, kKvFull1, kKvFree0, kKvFree1, kSFull0, kSFull1, kSFree0,
-  kSFree1, kPFull0, kPFull1, kPFree0, kPFree1, kODone, kOFree, kTokenDone0, kTokenDone1, kBarCount
+  kTokenReady0 = 0, kTokenReady1, kTokenDone0, kTokenDone1, kQFull, kQFree,
+  kKvFull0, kKvFull1, kKvFull2, kKvFree0, kKvFree1, kKvFree2,
+  kSFull0, kSFull1, kPFull0, kPFull1, kODone, kOFree, kQStageFree0, kQStageFree1, kQStageFree2, kBarCount
 };
 
 constexpr uint32_t kIdescQK = idesc_f16(64, 64, 1, 0, 0);
@@ -105,12 +117,26 @@ struct Shared {
   __device__ __forceinline__ int* scratch() const { return reinterpret_cast<int*>(ptr + kSmemMisc + 8); }
 };
 
-// ---- producer warps ---------------------------------------------------------------------------
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool live) {
-  // A masked slot is zero-filled (source size 0) so the tile never holds non-finite leftovers.
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(live ? 16 : 0));
+// Compile-time diagnostic: with SPARSE_MLA_TRACE defined, block 0 logs (event, value, SM clock)
+// in shared memory and copies the log out through `Params::scheduler` when it finishes.
+#ifdef SPARSE_MLA_TRACE
+// Three private logs (producer thread 0, MMA thread, softmax thread 0), each kTraceEntries / 3
+// entries of (event << 24 | value, clock); word 0..2 of the region hold the three counts.
+__device__ __forceinline__ void trace(const Shared& sm, int event, int value) {
+  if (blockIdx.x != 0) return;
+  const int role = threadIdx.x == 0 ? 2 : (threadIdx.x == kMmaWarp * 32 ? 1 : 0);
+  unsigned* log = reinterpret_cast<unsigned*>(sm.ptr + kSmemTrace);
+  const unsigned slot = log[role]++;
+  constexpr unsigned per_role = kTraceEntries / 3;
+  if (slot < per_role) {
+    log[4 + 2 * (role * per_role + slot)] = (unsigned(event) << 24) | (unsigned(value) & 0xffffffu);
+    log[5 + 2 * (role * per_role + slot)] = unsigned(clock64());
+  }
 }
+#define TRACE(sm, event, value) trace(sm, event, value)
+#else
+#define TRACE(sm, event, value) do {} while (0)
+#endif
 
 // A producer wait whose outcome is the same for all producer threads: if any of them gave up,
 // all of them leave (a thread that returned alone would strand the others at the next bar.sync).
@@ -127,162 +153,250 @@ __device__ __forceinline__ bool producer_wait(uint32_t bar, uint32_t parity, vol
   return failed == 0;
 }
 
+// True when the phase has completed already, with the same answer for all producer threads.
+__device__ __forceinline__ bool producer_poll(uint32_t bar, uint32_t parity) {
+  const uint32_t ok = mbar_test(bar, parity) ? 1u : 0u;
+  uint32_t all;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.u32 q, %1, 0;\n"
+      "bar.red.and.pred p, 1, %2, q;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n" : "=r"(all) : "r"(ok), "n"(kProducerThreads) : "memory");
+  return all != 0;
+}
+
 // A wait whose outcome is uniform across the calling warp (all 32 lanes must call it).
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
 }
 
+// ---- producer warps ---------------------------------------------------------------------------
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool live) {
+#ifdef SPARSE_MLA_EXPERIMENT_NO_COPY
+  return;
+#endif
+  // A masked slot is zero-filled (source size 0) so the tile never holds non-finite leftovers.
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(live ? 16 : 0));
+}
+
+// Resolve the 640 slots of `token` into row buffer `token_count & 1`, list its live chunks and
+// publish both to the other roles. Returns false when a wait gave up.
+__device__ __forceinline__ bool resolve_token(const Params& p, const Shared& sm, int token,
+                                              uint32_t token_count, int tid) {
+  const int lane = tid & 31;
+  const int buffer = token_count & 1;
+  int* rows = sm.rows(buffer);
+  TokenInfo* info = sm.info(buffer);
+  int* scratch = sm.scratch();
+  // The buffer is free once the softmax warps have finished the token that used it two tokens
+  // ago. (Barriers that one role may pass without the others keeping up exist once per buffer:
+  // a phase parity can only tell two consecutive phases apart.)
+  if (token_count >= 2 &&
+      !producer_wait(sm.bar(kTokenDone0 + buffer), ((token_count >> 1) & 1) ^ 1, sm.abort_flag())) return false;
+  const TokenGeometry g = token_geometry(p, token);
+  if (tid == 0) *scratch = kTopK;
+  producer_sync();
+  const int32_t* list = p.indices + (size_t)token * kTopK;
+  {
+    int first = kTopK;
+    for (int rank = tid; rank < kTopK; rank += kProducerThreads)
+      if (__ldg(list + rank) < 0) { first = rank; break; }
+    if (first < kTopK) atomicMin(scratch, first);
+  }
+  producer_sync();
+  const int first_negative = *scratch;
+  for (int slot = tid; slot < kSlots; slot += kProducerThreads)
+    rows[slot] = slot < kWindow
+        ? resolve_window_slot(p, g, token, slot)
+        : resolve_compressed_rank(p, g, token, slot - kWindow, __ldg(list + slot - kWindow), first_negative);
+  producer_sync();
+  if (tid < 32) {  // one warp lists the chunks that hold at least one live slot
+    int count = 0;
+    for (int chunk = 0; chunk < kMaxChunks; ++chunk) {
+      const bool live = rows[chunk * kChunkRows + lane] >= 0 || rows[chunk * kChunkRows + 32 + lane] >= 0;
+      if (__any_sync(0xffffffffu, live)) {
+        if (lane == 0) info->chunk[count] = (unsigned char)chunk;
+        ++count;
+      }
+    }
+    if (lane == 0) { info->token = token; info->chunks = count; }
+  }
+  producer_sync();
+  if (lane == 0) mbar_arrive(sm.bar(kTokenReady0 + buffer));
+  return true;
+}
+
 __device__ void producer_role(const Params& p, const Shared& sm) {
-  const int tid = threadIdx.x - kFirstProducerWarp * 32;  // 0..127
+  const int tid = threadIdx.x - kFirstProducerWarp * 32;
   const int lane = tid & 31;
   volatile int* abort_flag = sm.abort_flag();
-  uint32_t chunk_count = 0;  // live chunks handed to the MMA warp so far (all tokens)
+  const char* window_base = static_cast<const char*>(p.ori_kv);
+  const char* compressed_base = static_cast<const char*>(p.cmp_kv);
+  // Ring bookkeeping. A stage is released either by the MMA warp (a KV tile, kKvFree) or by the
+  // softmax warps (a Q tile, kQStageFree); each of those barriers advances only with its own
+  // kind of tile, so per stage we remember which barrier and which phase parity frees it next.
+  uint32_t ring = 0;  // tiles placed so far (all tokens): a Q tile per working token, then its chunks
+  uint32_t occupied = 0, last_is_q = 0, last_parity = 0, next_parity_kv = 0, next_parity_q = 0;
   uint32_t token_count = 0;
+  if (blockIdx.x < p.tokens && !resolve_token(p, sm, blockIdx.x, 0, tid)) return;
   for (int token = blockIdx.x; token < p.tokens; token += gridDim.x, ++token_count) {
-    const int buffer = token_count & 1;
-    int* rows = sm.rows(buffer);
-    TokenInfo* info = sm.info(buffer);
-    int* scratch = sm.scratch();
-
-    // Resolve the 640 slots once the softmax warps have finished the token that used this
-    // buffer two tokens ago. (Barriers that a role may pass without the others keeping up are
-    // kept per buffer: a phase parity can only tell apart two consecutive phases.)
-    if (token_count >= 2 &&
-        !producer_wait(sm.bar(kTokenDone0 + buffer), ((token_count >> 1) & 1) ^ 1, abort_flag)) return;
-    const TokenGeometry g = token_geometry(p, token);
-    if (tid == 0) *scratch = kTopK;
-    producer_sync();
-    const int32_t* list = p.indices + (size_t)token * kTopK;
-    {
-      int first = kTopK;
-      for (int rank = tid; rank < kTopK; rank += kProducerThreads)
-        if (__ldg(list + rank) < 0) { first = rank; break; }
-      if (first < kTopK) atomicMin(scratch, first);
-    }
-    producer_sync();
-    const int first_negative = *scratch;
-    for (int slot = tid; slot < kSlots; slot += kProducerThreads)
-      rows[slot] = slot < kWindow
-          ? resolve_window_slot(p, g, token, slot)
-          : resolve_compressed_rank(p, g, token, slot - kWindow, __ldg(list + slot - kWindow), first_negative);
-    producer_sync();
-    if (tid < 32) {  // one warp lists the chunks that hold at least one live slot
-      int count = 0;
-      for (int chunk = 0; chunk < kMaxChunks; ++chunk) {
-        const bool live = rows[chunk * kChunkRows + lane] >= 0 || rows[chunk * kChunkRows + 32 + lane] >= 0;
-        if (__any_sync(0xffffffffu, live)) {
-          if (lane == 0) info->chunk[count] = (unsigned char)chunk;
-          ++count;
-        }
-      }
-      if (lane == 0) { info->token = token; info->chunks = count; }
-    }
-    producer_sync();
+    const int* rows = sm.rows(token_count & 1);
+    const TokenInfo* info = sm.info(token_count & 1);
     const int chunks = info->chunks;
-
-    // Q tile: wait until the previous token's last QK has read it.
-    if (!producer_wait(sm.bar(kQFree), (token_count & 1) ^ 1, abort_flag)) return;
-    if (chunks > 0) {
-      const char* q = static_cast<const char*>(p.q) + (size_t)token * kHeads * kRowBytes;
-      const int unit = tid & 63;
-      for (int r = tid >> 6; r < kHeads; r += kProducerThreads / 64)
-        cp_async16(sm.base + kSmemQ + swizzled(r, unit), q + (size_t)r * kRowBytes + unit * 16, true);
-      asm volatile("cp.async.commit_group;\n" ::: "memory");
-      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-      fence_proxy_async();
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(sm.bar(kQFull0 + buffer));
-
-    const char* window_base = static_cast<const char*>(p.ori_kv);
-    const char* compressed_base = static_cast<const char*>(p.cmp_kv);
-    for (int i = 0; i < chunks; ++i, ++chunk_count) {
-      const int stage = chunk_count & 1;
-      if (!producer_wait(sm.bar(kKvFree0 + stage), ((chunk_count >> 1) & 1) ^ 1, abort_flag)) return;
-      const int chunk = info->chunk[i];
+    const char* q = static_cast<const char*>(p.q) + (size_t)token * kHeads * kRowBytes;
+    int pending = -1;  // stage whose copies are in flight and not yet announced
+    for (int item = chunks > 0 ? -1 : 0; item < chunks; ++item, ++ring) {
+      const uint32_t stage = ring % kStages, bit = 1u << stage;
+      const bool is_q = item < 0;
+      if (occupied & bit) {
+        const uint32_t bar = sm.bar(((last_is_q & bit) ? kQStageFree0 : kKvFree0) + stage);
+        const uint32_t parity = (last_parity >> stage) & 1u;
+        if (pending >= 0 && !producer_poll(bar, parity)) {
+          // The ring is full: announce the copies in flight before blocking on a free stage.
+          asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+          fence_proxy_async();
+          __syncwarp();
+          if (tid == 0) TRACE(sm, 5, item - 1);
+          if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + pending));
+          pending = -1;
+        }
+        if (!producer_wait(bar, parity, abort_flag)) return;
+      }
+      occupied |= bit;
+      const uint32_t next_parity = is_q ? next_parity_q : next_parity_kv;
+      last_parity = (last_parity & ~bit) | (next_parity & bit);
+      if (is_q) { next_parity_q ^= bit; last_is_q |= bit; } else { next_parity_kv ^= bit; last_is_q &= ~bit; }
+      if (tid == 0) TRACE(sm, 4, item);
       const uint32_t tile = sm.base + kSmemKv + stage * kTileBytes;
       const int unit = tid & 63;
-      for (int r = tid >> 6; r < kChunkRows; r += kProducerThreads / 64) {
-        const int slot = chunk * kChunkRows + r;
-        const int row = rows[slot];
-        const char* base = slot < kWindow ? window_base : compressed_base;
-        cp_async16(tile + swizzled(r, unit), base + (size_t)(row < 0 ? 0 : row) * kRowBytes + unit * 16, row >= 0);
+      if (is_q) {
+        for (int r = tid >> 6; r < kHeads; r += kProducerThreads / 64)
+          cp_async16(tile + swizzled(r, unit), q + (size_t)r * kRowBytes + unit * 16, true);
+      } else {
+        const int chunk = info->chunk[item];
+        for (int r = tid >> 6; r < kChunkRows; r += kProducerThreads / 64) {
+          const int slot = chunk * kChunkRows + r;
+          const int row = rows[slot];
+          const char* base = slot < kWindow ? window_base : compressed_base;
+          cp_async16(tile + swizzled(r, unit), base + (size_t)(row < 0 ? 0 : row) * kRowBytes + unit * 16, row >= 0);
+        }
       }
       asm volatile("cp.async.commit_group;\n" ::: "memory");
+      if (pending >= 0) {  // the previous tile has landed once at most one group is outstanding
+        asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        fence_proxy_async();
+        __syncwarp();
+        if (tid == 0) TRACE(sm, 5, item - 1);
+        if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + pending));
+      }
+      pending = int(stage);
+    }
+    // Resolve the next token while the last copies are in flight.
+    const int next = token + gridDim.x;
+    if (next < p.tokens) {
+      if (tid == 0) TRACE(sm, 1, next);
+      if (!resolve_token(p, sm, next, token_count + 1, tid)) return;
+      if (tid == 0) TRACE(sm, 2, next);
+    }
+    if (pending >= 0) {
       asm volatile("cp.async.wait_group 0;\n" ::: "memory");
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + stage));
+      if (tid == 0) TRACE(sm, 5, chunks - 1);
+      if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + pending));
     }
   }
 }
 
 // ---- MMA warp (one thread) --------------------------------------------------------------------
 
-__device__ __forceinline__ void issue_qk(const Shared& sm, uint32_t tmem, int stage, int s_buffer) {
-  const uint32_t d = tmem + kTmemS + s_buffer * 64 + (uint32_t(16 * s_buffer) << 16);
-  const uint32_t q = sm.base + kSmemQ, x = sm.base + kSmemKv + stage * kTileBytes;
-#pragma unroll
-  for (int k = 0; k < kFeatures / 16; ++k) {
-    const uint32_t offset = (k >> 2) * kBlockBytes + (k & 3) * 32;
-    mma_ss(d, smem_desc_sw128(q + offset, 16, 1024), smem_desc_sw128(x + offset, 16, 1024), kIdescQK, k > 0);
+// Compile-time unrolled issue loops: every operand offset and accumulate flag is an immediate,
+// so the issuing thread spends a couple of instructions per MMA and stays ahead of the pipe.
+template <int K>
+__device__ __forceinline__ void issue_qk_steps(uint32_t s_tmem, uint32_t q_tmem, uint64_t x_desc) {
+  if constexpr (K < kFeatures / 16) {
+    constexpr uint32_t half = (K >> 4) * kHalfLanes;
+    constexpr uint32_t offset = (K >> 2) * kBlockBytes + (K & 3) * 32;
+    mma_ts_c<(K & 15) != 0>(s_tmem + half, q_tmem + (K & 15) * 8 + half, x_desc + (offset >> 4), kIdescQK);
+    issue_qk_steps<K + 1>(s_tmem, q_tmem, x_desc);
   }
 }
 
-__device__ __forceinline__ void issue_pv(const Shared& sm, uint32_t tmem, int stage, int p_buffer, bool accumulate) {
-  const uint32_t prob = sm.base + kSmemP + p_buffer * kBlockBytes, x = sm.base + kSmemKv + stage * kTileBytes;
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const uint32_t d = tmem + kTmemO + (uint32_t(16 * half) << 16);
-#pragma unroll
-    for (int k = 0; k < kChunkRows / 16; ++k) {
-      // A: P[64 heads x 16 rows], K-major. B: X[16 rows x 256 features], features contiguous:
-      // four 64-feature blocks kBlockBytes apart, 8-row groups 1024 bytes apart.
-      mma_ss(d, smem_desc_sw128(prob + k * 32, 16, 1024),
-             smem_desc_sw128(x + half * 4 * kBlockBytes + k * 2048, kBlockBytes, 1024), kIdescPV,
-             accumulate || k > 0);
-    }
+// S[buffer] = Q X^T for one 64-row tile, as two partial products: features 0-255 in lane half 0,
+// 256-511 in lane half 1. A = Q from tensor memory (8 columns of BF16 pairs per K=16 step).
+__device__ __forceinline__ void issue_qk(const Shared& sm, uint32_t tmem, int stage, int buffer) {
+  const uint64_t x_desc = smem_desc_sw128(sm.base + kSmemKv + stage * kTileBytes, 16, 1024);
+  issue_qk_steps<0>(tmem + kTmemS + buffer * 64, tmem + kTmemQ, x_desc);
+}
+
+template <int I, bool kFirst>
+__device__ __forceinline__ void issue_pv_steps(uint32_t o_tmem, uint32_t p_tmem, uint64_t x_desc) {
+  if constexpr (I < 2 * (kChunkRows / 16)) {
+    constexpr int h = I / (kChunkRows / 16), k = I % (kChunkRows / 16);
+    constexpr uint32_t half = h * kHalfLanes;
+    constexpr uint32_t offset = h * 4 * kBlockBytes + k * 2048;
+    mma_ts_c<!(kFirst && k == 0)>(o_tmem + half, p_tmem + k * 8 + half, x_desc + (offset >> 4), kIdescPV);
+    issue_pv_steps<I + 1, kFirst>(o_tmem, p_tmem, x_desc);
   }
+}
+
+// O += P X for one 64-row tile: features 0-255 in lane half 0, 256-511 in lane half 1.
+// A = P from tensor memory (written to both halves by the softmax threads); B = X with features
+// contiguous: four 64-feature blocks kBlockBytes apart, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ void issue_pv(const Shared& sm, uint32_t tmem, int stage, int buffer, bool accumulate) {
+  const uint64_t x_desc = smem_desc_sw128(sm.base + kSmemKv + stage * kTileBytes, kBlockBytes, 1024);
+  if (accumulate) issue_pv_steps<0, false>(tmem + kTmemO, tmem + kTmemS + buffer * 64, x_desc);
+  else issue_pv_steps<0, true>(tmem + kTmemO, tmem + kTmemS + buffer * 64, x_desc);
 }
 
 __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
   volatile int* abort_flag = sm.abort_flag();
-  uint32_t chunk_count = 0, token_count = 0, working_tokens = 0;
+  // `ring` counts tiles in the shared ring (a Q tile per working token, then its chunks);
+  // `chunk_count` counts KV chunks only and selects the S / P buffer.
+  uint32_t ring = 0, chunk_count = 0, token_count = 0, working_tokens = 0;
   for (int token = blockIdx.x; token < p.tokens; token += gridDim.x, ++token_count) {
-    if (!mbar_wait(sm.bar(kQFull0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
+    if (!mbar_wait(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
     const int chunks = sm.info(token_count & 1)->chunks;
-    if (chunks == 0) { mbar_arrive(sm.bar(kQFree)); continue; }
-    tc_fence_after_sync();
-    // First QK of the token.
-    {
-      const uint32_t n = chunk_count, slot = n & 1, use = (n >> 1) & 1;
-      if (!mbar_wait(sm.bar(kKvFull0 + slot), use, abort_flag)) return;
-      if (!mbar_wait(sm.bar(kSFree0 + slot), use ^ 1, abort_flag)) return;
+    if (chunks == 0) continue;
+    ++ring;  // the token's Q tile: consumed by the softmax warps
+    if (!mbar_wait(sm.bar(kQFull), working_tokens & 1, abort_flag)) return;
+    {  // first QK of the token
+      const uint32_t stage = ring % kStages, use = ring / kStages;
+      if (!mbar_wait(sm.bar(kKvFull0 + stage), use & 1, abort_flag)) return;
       tc_fence_after_sync();
-      issue_qk(sm, tmem, slot, slot);
-      mma_commit(sm.bar(kSFull0 + slot));
+      TRACE(sm, 13, 0);
+      issue_qk(sm, tmem, stage, chunk_count & 1);
+      mma_commit(sm.bar(kSFull0 + (chunk_count & 1)));
       if (chunks == 1) mma_commit(sm.bar(kQFree));
+      TRACE(sm, 14, 0);
     }
-    for (int i = 0; i < chunks; ++i, ++chunk_count) {
+    for (int i = 0; i < chunks; ++i, ++chunk_count, ++ring) {
       if (i + 1 < chunks) {  // QK of the next chunk runs while the softmax warps work on this one
-        const uint32_t n = chunk_count + 1, slot = n & 1, use = (n >> 1) & 1;
-        if (!mbar_wait(sm.bar(kKvFull0 + slot), use, abort_flag)) return;
-        if (!mbar_wait(sm.bar(kSFree0 + slot), use ^ 1, abort_flag)) return;
+        const uint32_t n = ring + 1, stage = n % kStages, use = n / kStages, c = chunk_count + 1;
+        if (!mbar_wait(sm.bar(kKvFull0 + stage), use & 1, abort_flag)) return;
         tc_fence_after_sync();
-        issue_qk(sm, tmem, slot, slot);
-        mma_commit(sm.bar(kSFull0 + slot));
+        TRACE(sm, 13, i + 1);
+        // The S buffer it overwrites held P of chunk c - 2, whose PV was issued before: in order.
+        issue_qk(sm, tmem, stage, c & 1);
+        mma_commit(sm.bar(kSFull0 + (c & 1)));
         if (i + 2 == chunks) mma_commit(sm.bar(kQFree));
+        TRACE(sm, 14, i + 1);
       }
-      const uint32_t slot = chunk_count & 1, use = (chunk_count >> 1) & 1;
+      const uint32_t stage = ring % kStages, c = chunk_count;
       if (i == 0) {  // the previous token's epilogue must have read O
         if (!mbar_wait(sm.bar(kOFree), (working_tokens & 1) ^ 1, abort_flag)) return;
       }
-      if (!mbar_wait(sm.bar(kPFull0 + slot), use, abort_flag)) return;
+      TRACE(sm, 10, i);
+      if (!mbar_wait(sm.bar(kPFull0 + (c & 1)), (c >> 1) & 1, abort_flag)) return;
       tc_fence_after_sync();
-      issue_pv(sm, tmem, slot, slot, i > 0);
-      mma_commit(sm.bar(kKvFree0 + slot));
-      mma_commit(sm.bar(kPFree0 + slot));
+      TRACE(sm, 11, i);
+      issue_pv(sm, tmem, stage, c & 1, i > 0);
+      mma_commit(sm.bar(kKvFree0 + stage));
       mma_commit(sm.bar(kODone));
+      TRACE(sm, 12, i);
     }
     ++working_tokens;
   }
@@ -290,56 +404,102 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
 
 // ---- softmax / correction / epilogue warps ----------------------------------------------------
 
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Copy this thread's half row of Q (256 BF16 = 128 words) from a staged shared tile (same
+// swizzled layout as a KV tile: row = head) to tensor memory.
+__device__ __forceinline__ void load_q_half_row(const Shared& sm, uint32_t tmem_q, int stage, int head, int half) {
+  const unsigned char* tile = sm.ptr + kSmemKv + stage * kTileBytes;
+#pragma unroll
+  for (int block = 0; block < 4; ++block) {
+    uint32_t words[32];
+#pragma unroll
+    for (int unit = 0; unit < 8; ++unit) {
+      const uint4 v = *reinterpret_cast<const uint4*>(tile + swizzled(head, (half * 4 + block) * 8 + unit));
+      words[unit * 4 + 0] = v.x; words[unit * 4 + 1] = v.y; words[unit * 4 + 2] = v.z; words[unit * 4 + 3] = v.w;
+    }
+    tmem_st16(tmem_q + block * 32, *reinterpret_cast<uint32_t(*)[16]>(&words[0]));
+    tmem_st16(tmem_q + block * 32 + 16, *reinterpret_cast<uint32_t(*)[16]>(&words[16]));
+  }
+  tmem_wait_st();
+}
+
 __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int parity = lane >> 4;                 // which S buffer / which half of O this lane owns
+  const int half = lane >> 4;
   const int head = warp * 16 + (lane & 15);
   const uint32_t lane_base = uint32_t(warp * 32) << 16;
   volatile int* abort_flag = sm.abort_flag();
   const float sink = __ldg(p.sinks + head) * 1.4426950408889634f;  // log2 domain
-  uint32_t chunk_count = 0, token_count = 0, pv_waited = 0;
+  uint32_t ring = 0, chunk_count = 0, token_count = 0, pv_waited = 0, q_loads = 0;
   __nv_bfloat16* out_base = static_cast<__nv_bfloat16*>(p.out);
 
+  // Wait for a token's row list; if it has work, move its Q into tensor memory once the QKs of
+  // the previous working token have finished reading the old one. Returns false on a failed wait.
+  auto prepare = [&](int token, uint32_t count) -> bool {
+    if (!warp_wait(sm.bar(kTokenReady0 + (count & 1)), (count >> 1) & 1, abort_flag)) return false;
+    if (sm.info(count & 1)->chunks == 0) return true;
+    const uint32_t stage = ring % kStages, use = ring / kStages;
+    if (!warp_wait(sm.bar(kKvFull0 + stage), use & 1, abort_flag)) return false;
+    if (q_loads > 0 && !warp_wait(sm.bar(kQFree), (q_loads - 1) & 1, abort_flag)) return false;
+    tc_fence_after_sync();
+    load_q_half_row(sm, tmem + kTmemQ + lane_base, stage, head, half);
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) {
+      mbar_arrive(sm.bar(kQStageFree0 + stage));
+      mbar_arrive(sm.bar(kQFull));
+    }
+    ++q_loads;
+    ++ring;
+    return true;
+  };
+
+  if (blockIdx.x < p.tokens && !prepare(blockIdx.x, 0)) return;
   for (int token = blockIdx.x; token < p.tokens; token += gridDim.x, ++token_count) {
-    if (!warp_wait(sm.bar(kQFull0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
     const TokenInfo* info = sm.info(token_count & 1);
     const int* rows = sm.rows(token_count & 1);
     const int chunks = info->chunks;
-    __nv_bfloat16* out = out_base + ((size_t)token * kHeads + head) * kFeatures + parity * 256;
+    const int next = token + gridDim.x;
+    __nv_bfloat16* out = out_base + ((size_t)token * kHeads + head) * kFeatures + half * 256;
     if (chunks == 0) {  // nothing visible: the output row is zero whatever the sink
       for (int i = 0; i < 256; i += 8) *reinterpret_cast<uint4*>(out + i) = make_uint4(0, 0, 0, 0);
+      if (next < p.tokens && !prepare(next, token_count + 1)) return;
       __syncwarp();
       if (lane == 0) mbar_arrive(sm.bar(kTokenDone0 + (token_count & 1)));
       continue;
     }
     float run_max = sink, run_sum = 1.f;  // the sink's own weight exp2(sink - run_max)
-    for (int i = 0; i < chunks; ++i, ++chunk_count) {
-      const uint32_t slot = chunk_count & 1, use = (chunk_count >> 1) & 1;
-      const bool owner = parity == int(slot);
+    for (int i = 0; i < chunks; ++i, ++chunk_count, ++ring) {
+      const uint32_t buffer = chunk_count & 1;
       const int chunk = info->chunk[i];
       const unsigned live_lo = __ballot_sync(0xffffffffu, rows[chunk * kChunkRows + lane] >= 0);
       const unsigned live_hi = __ballot_sync(0xffffffffu, rows[chunk * kChunkRows + 32 + lane] >= 0);
+      const uint32_t s_addr = tmem + kTmemS + buffer * 64 + lane_base;
 
-      if (!warp_wait(sm.bar(kSFull0 + slot), use, abort_flag)) return;
+      if (threadIdx.x == 0) TRACE(sm, 20, i);
+      if (!warp_wait(sm.bar(kSFull0 + buffer), (chunk_count >> 1) & 1, abort_flag)) return;
+      if (threadIdx.x == 0) TRACE(sm, 21, i);
       tc_fence_after_sync();
-      uint32_t raw[64];
+      float s[64];
 #pragma unroll
       for (int c = 0; c < 64; c += 16)
-        tmem_ld16(tmem + kTmemS + slot * 64 + c + lane_base, *reinterpret_cast<uint32_t(*)[16]>(&raw[c]));
+        tmem_ld16(s_addr + c, *reinterpret_cast<uint32_t(*)[16]>(&s[c]));
       tmem_wait_ld();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sm.bar(kSFree0 + slot));
 
-      float s[64];
-      float chunk_max = -INFINITY;
+      // Add the partner half's partial product, scale, mask.
+      float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int j = 0; j < 64; ++j) {
+        const float total = s[j] + __shfl_xor_sync(0xffffffffu, s[j], 16);
         const bool live = ((j < 32 ? live_lo : live_hi) >> (j & 31)) & 1u;
-        s[j] = (owner && live) ? __uint_as_float(raw[j]) * p.scale_log2 : -INFINITY;
-        chunk_max = fmaxf(chunk_max, s[j]);
+        s[j] = live ? total * p.scale_log2 : -INFINITY;
+        partial_max[j & 3] = fmaxf(partial_max[j & 3], s[j]);
       }
-      chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, 16));
+      const float chunk_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3]));
       // The running maximum only moves when it is exceeded by more than 8 (a factor 256), so the
       // accumulator is rescaled rarely; probabilities stay below 2^8 and all terms of one head
       // share the same reference, which cancels in the final division.
@@ -348,47 +508,38 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
         alpha = exp2f(run_max - chunk_max);
         run_max = chunk_max;
       }
-      if (__any_sync(0xffffffffu, alpha != 1.f)) {
-        if (i > 0) {  // O holds earlier chunks: the previous PV must have landed
-          while (pv_waited < chunk_count) {
-            if (!warp_wait(sm.bar(kODone), pv_waited & 1, abort_flag)) return;
-            ++pv_waited;
-          }
-          tc_fence_after_sync();
+      if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        // O holds earlier chunks: the previous PV must have landed before it is rescaled.
+        while (pv_waited < chunk_count) {
+          if (!warp_wait(sm.bar(kODone), pv_waited & 1, abort_flag)) return;
+          ++pv_waited;
+        }
+        tc_fence_after_sync();
 #pragma unroll 1
-          for (int c = 0; c < 256; c += 16) {
-            uint32_t o[16];
-            tmem_ld16(tmem + kTmemO + c + lane_base, o);
-            tmem_wait_ld();
+        for (int c = 0; c < 256; c += 16) {
+          uint32_t o[16];
+          tmem_ld16(tmem + kTmemO + c + lane_base, o);
+          tmem_wait_ld();
 #pragma unroll
-            for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-            tmem_st16(tmem + kTmemO + c + lane_base, o);
-          }
-          tmem_wait_st();
-          tc_fence_before_sync();
+          for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+          tmem_st16(tmem + kTmemO + c + lane_base, o);
         }
       }
-      float sum = 0.f;
+      float partial_sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < 64; ++j) { s[j] = exp2f(s[j] - run_max); sum += s[j]; }
-      sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-      run_sum = run_sum * alpha + sum;
+      for (int j = 0; j < 64; ++j) { s[j] = exp2f(s[j] - run_max); partial_sum[j & 3] += s[j]; }
+      run_sum = run_sum * alpha + ((partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]));
 
-      if (!warp_wait(sm.bar(kPFree0 + slot), use ^ 1, abort_flag)) return;
-      if (owner) {
-        unsigned char* row = sm.ptr + kSmemP + slot * kBlockBytes + head * 128;
+      // P as BF16 pairs over the start of this S buffer, in this thread's own lane half.
 #pragma unroll
-        for (int unit = 0; unit < 8; ++unit) {
-          uint4 packed;
-          __nv_bfloat162 v;
-          v = __floats2bfloat162_rn(s[unit * 8 + 0], s[unit * 8 + 1]); packed.x = *reinterpret_cast<uint32_t*>(&v);
-          v = __floats2bfloat162_rn(s[unit * 8 + 2], s[unit * 8 + 3]); packed.y = *reinterpret_cast<uint32_t*>(&v);
-          v = __floats2bfloat162_rn(s[unit * 8 + 4], s[unit * 8 + 5]); packed.z = *reinterpret_cast<uint32_t*>(&v);
-          v = __floats2bfloat162_rn(s[unit * 8 + 6], s[unit * 8 + 7]); packed.w = *reinterpret_cast<uint32_t*>(&v);
-          *reinterpret_cast<uint4*>(row + ((unit ^ (head & 7)) << 4)) = packed;
-        }
-        fence_proxy_async();
+      for (int c = 0; c < 2; ++c) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) packed[e] = pack_bf16(s[c * 32 + 2 * e], s[c * 32 + 2 * e + 1]);
+        tmem_st16(s_addr + c * 16, packed);
       }
+      tmem_wait_st();
+      tc_fence_before_sync();
       // Observe the previous chunk's PV completion before releasing this P: the PV barrier then
       // never runs more than one phase ahead of this warp.
       while (pv_waited < chunk_count) {
@@ -396,35 +547,41 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
         ++pv_waited;
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(sm.bar(kPFull0 + slot));
+      if (threadIdx.x == 0) TRACE(sm, 22, i);
+      if (lane == 0) mbar_arrive(sm.bar(kPFull0 + buffer));
     }
+
+    // Next token's Q goes to tensor memory while the last PV of this one runs.
+    if (next < p.tokens && !prepare(next, token_count + 1)) return;
+
     // ---- epilogue: O / denominator -> BF16 -> global ------------------------------------------
     while (pv_waited < chunk_count) {
       if (!warp_wait(sm.bar(kODone), pv_waited & 1, abort_flag)) return;
       ++pv_waited;
     }
     tc_fence_after_sync();
+    if (threadIdx.x == 0) TRACE(sm, 23, token);
     const float inverse = 1.f / run_sum;
 #pragma unroll 1
-    for (int c = 0; c < 256; c += 16) {
-      uint32_t o[16];
-      tmem_ld16(tmem + kTmemO + c + lane_base, o);
+    for (int c = 0; c < 256; c += 64) {
+      uint32_t o[64];
+#pragma unroll
+      for (int q = 0; q < 64; q += 16)
+        tmem_ld16(tmem + kTmemO + c + q + lane_base, *reinterpret_cast<uint32_t(*)[16]>(&o[q]));
       tmem_wait_ld();
-      uint4 lo, hi;
-      __nv_bfloat162 v;
-      v = __floats2bfloat162_rn(__uint_as_float(o[0]) * inverse, __uint_as_float(o[1]) * inverse); lo.x = *reinterpret_cast<uint32_t*>(&v);
-      v = __floats2bfloat162_rn(__uint_as_float(o[2]) * inverse, __uint_as_float(o[3]) * inverse); lo.y = *reinterpret_cast<uint32_t*>(&v);
-      v = __floats2bfloat162_rn(__uint_as_float(o[4]) * inverse, __uint_as_float(o[5]) * inverse); lo.z = *reinterpret_cast<uint32_t*>(&v);
-      v = __floats2bfloat162_rn(__uint_as_float(o[6]) * inverse, __uint_as_float(o[7]) * inverse); lo.w = *reinterpret_cast<uint32_t*>(&v);
-      v = __floats2bfloat162_rn(__uint_as_float(o[8]) * inverse, __uint_as_float(o[9]) * inverse); hi.x = *reinterpret_cast<uint32_t*>(&v);
-      v = __floats2bfloat162_rn(__uint_as_float(o[10]) * inverse, __uint_as_float(o[11]) * inverse); hi.y = *reinterpret_cast<uint32_t*>(&v);
-      v = __floats2bfloat162_rn(__uint_as_float(o[12]) * inverse, __uint_as_float(o[13]) * inverse); hi.z = *reinterpret_cast<uint32_t*>(&v);
-      v = __floats2bfloat162_rn(__uint_as_float(o[14]) * inverse, __uint_as_float(o[15]) * inverse); hi.w = *reinterpret_cast<uint32_t*>(&v);
-      *reinterpret_cast<uint4*>(out + c) = lo;
-      *reinterpret_cast<uint4*>(out + c + 8) = hi;
+#pragma unroll
+      for (int q = 0; q < 64; q += 8) {
+        uint4 v;
+        v.x = pack_bf16(__uint_as_float(o[q + 0]) * inverse, __uint_as_float(o[q + 1]) * inverse);
+        v.y = pack_bf16(__uint_as_float(o[q + 2]) * inverse, __uint_as_float(o[q + 3]) * inverse);
+        v.z = pack_bf16(__uint_as_float(o[q + 4]) * inverse, __uint_as_float(o[q + 5]) * inverse);
+        v.w = pack_bf16(__uint_as_float(o[q + 6]) * inverse, __uint_as_float(o[q + 7]) * inverse);
+        *reinterpret_cast<uint4*>(out + c + q) = v;
+      }
     }
     tc_fence_before_sync();
     __syncwarp();
+    if (threadIdx.x == 0) TRACE(sm, 24, token);
     if (lane == 0) {
       mbar_arrive(sm.bar(kOFree));
       mbar_arrive(sm.bar(kTokenDone0 + (token_count & 1)));
@@ -445,12 +602,14 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm.ptr + kSmemMisc);
 
   if (threadIdx.x == 0) {
-    const int counts[kBarCount] = {kProducerWarps, kProducerWarps, 1, kProducerWarps, kProducerWarps, 1, 1,
-                                   1, 1, kSoftmaxWarps, kSoftmaxWarps, kSoftmaxWarps, kSoftmaxWarps, 1, 1,
-                                   1, kSoftmaxWarps, kSoftmaxWarps, kSoftmaxWarps};
+    const int P = kProducerWarps, S = kSoftmaxWarps;
+    const int counts[kBarCount] = {P, P, S, S, S, 1, P, P, P, 1, 1, 1, 1, 1, S, S, 1, S, S, S, S};
     for (int i = 0; i < kBarCount; ++i) mbar_init(sm.bar(i), counts[i]);
     mbar_fence_init();
     *sm.abort_flag() = 0;
+#ifdef SPARSE_MLA_TRACE
+    for (int i = 0; i < 4; ++i) reinterpret_cast<unsigned*>(sm.ptr + kSmemTrace)[i] = 0;
+#endif
   }
   if (warp == kMmaWarp) { tmem_alloc(smem_u32(tmem_slot), kTmemColumns); tmem_relinquish(); }
   tc_fence_before_sync();
@@ -472,6 +631,13 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
   __syncthreads();
   if (threadIdx.x == 0 && *sm.abort_flag() != 0) report(p, kStatusWaitExpired, blockIdx.x, 0);
   if (warp == kMmaWarp) tmem_dealloc(tmem, kTmemColumns);
+#ifdef SPARSE_MLA_TRACE
+  if (blockIdx.x == 0) {
+    const unsigned* log = reinterpret_cast<const unsigned*>(sm.ptr + kSmemTrace);
+    unsigned* dst = reinterpret_cast<unsigned*>(p.scheduler);
+    for (int i = threadIdx.x; i < 4 + 2 * kTraceEntries; i += blockDim.x) dst[i] = log[i];
+  }
+#endif
 }
 
 inline int launch(const Params& p, cudaStream_t stream, int multiprocessors) {
