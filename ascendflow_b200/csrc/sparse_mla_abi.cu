@@ -103,6 +103,7 @@ bool fill(Params& p, void* q, void* ori_kv, void* cmp_kv, void* indices, void* o
   p.cmp_page = int32_t(CMP_PAGE); p.ratio = int32_t(kPage / CMP_PAGE);
   p.ori_blocks = int32_t(ORI_BLOCKS); p.cmp_blocks = int32_t(CMP_BLOCKS);
   p.scale_log2 = 0.044194173824159216f * 1.4426950408889634f;  // 512^-0.5 * log2(e)
+  p.token_group = 1;
   return true;
 }
 

@@ -56,6 +56,7 @@ struct Params {
   int32_t ori_blocks;
   int32_t cmp_blocks;
   float scale_log2;          // 512^-0.5 * log2(e)
+  int32_t token_group;       // consecutive tokens a persistent block takes per round (>= 1)
 };
 
 struct TokenGeometry {

@@ -5,9 +5,10 @@
 // walks the token's live 64-row chunks (window rows first, then the compressed ranks in list
 // order, as the reference does: examples/sparse_attention/attention.py:42-64, 147-207):
 //
-//   producer warps   resolve slot -> physical row (sparse_mla_common.cuh) one token ahead, then
-//                    gather the rows with 16-byte cp.async into a three-stage ring of
-//                    128-byte-swizzled shared tiles. A row is fetched once and serves as K and V.
+//   resolver warp    resolves slot -> physical row (sparse_mla_common.cuh) up to two tokens ahead.
+//   producer warps   gather the token's Q tile and then its rows with 16-byte cp.async into a
+//                    three-stage ring of 128-byte-swizzled shared tiles. A row is fetched once
+//                    and serves as K and V.
 //   MMA warp         one thread issues S = Q X^T and O += P X. Q and P are read from tensor
 //                    memory, X from the shared tile (K-major for QK, MN-major for PV).
 //   softmax warps    move the token's Q into tensor memory, tcgen05.ld S, joint online softmax
@@ -46,8 +47,9 @@ using namespace sm100;
 constexpr int kSoftmaxWarps = 4;
 constexpr int kProducerWarps = 8;
 constexpr int kMmaWarp = kSoftmaxWarps;                     // warp index 4
-constexpr int kFirstProducerWarp = kSoftmaxWarps + 1;
-constexpr int kThreads = 32 * (kSoftmaxWarps + 1 + kProducerWarps);
+constexpr int kResolverWarp = kSoftmaxWarps + 1;            // warp index 5
+constexpr int kFirstProducerWarp = kSoftmaxWarps + 2;
+constexpr int kThreads = 32 * (kSoftmaxWarps + 2 + kProducerWarps);
 constexpr int kProducerThreads = 32 * kProducerWarps;
 
 constexpr int kChunkRows = 64;
@@ -61,13 +63,14 @@ constexpr int kSmemKv = 0;
 constexpr int kSmemRows = kSmemKv + kStages * kTileBytes;   // int[2][640]
 constexpr int kSmemInfo = kSmemRows + 2 * kSlots * 4;       // TokenInfo[2]
 constexpr int kSmemBars = kSmemInfo + 2 * 64;               // mbarriers
-constexpr int kSmemMisc = kSmemBars + 32 * 8;               // tmem slot, abort flag, scratch
+constexpr int kSmemMisc = kSmemBars + 32 * 8;               // tmem slot, abort flag
+constexpr int kSmemStore = kSmemMisc + 64;                  // per softmax warp: 32 x 128-byte staging rows
 #ifdef SPARSE_MLA_TRACE
 constexpr int kTraceEntries = 2400;
-constexpr int kSmemTrace = kSmemMisc + 64;
+constexpr int kSmemTrace = kSmemStore + kSoftmaxWarps * 4096;
 constexpr int kSmemBytes = kSmemTrace + 16 + kTraceEntries * 8 + 1024;
 #else
-constexpr int kSmemBytes = kSmemMisc + 64 + 1024;           // + slack for the 1024-byte alignment
+constexpr int kSmemBytes = kSmemStore + kSoftmaxWarps * 4096 + 1024;  // + slack for the 1024-byte alignment
 #endif
 
 constexpr uint32_t kTmemColumns = 512;
@@ -115,6 +118,26 @@ struct Shared {
     return reinterpret_cast<volatile int*>(ptr + kSmemMisc + 4);
   }
   __device__ __forceinline__ int* scratch() const { return reinterpret_cast<int*>(ptr + kSmemMisc + 8); }
+};
+
+// The tokens of one persistent block, in order. Blocks take `group` consecutive tokens per round
+// (round r, block b: tokens (r * grid + b) * group ...), so that a block's successive tokens
+// share most of their window rows in L2 while different blocks read different windows at any one
+// time. Every role of a block walks the same sequence.
+struct TokenWalk {
+  int block, grid, group, tokens, k;
+  __device__ __forceinline__ explicit TokenWalk(const Params& p)
+      : block(blockIdx.x), grid(gridDim.x), group(p.token_group), tokens(p.tokens), k(0) {}
+  __device__ __forceinline__ int next() {  // next token of this block, or -1 when done
+    while (true) {
+      const int round = k / group;
+      if ((long long)round * grid * group >= tokens) return -1;
+      const int token = (round * grid + block) * group + k % group;
+      ++k;
+      if (token < tokens) return token;
+    }
+  }
+  __device__ __forceinline__ int peek() const { TokenWalk copy = *this; return copy.next(); }
 };
 
 // Compile-time diagnostic: with SPARSE_MLA_TRACE defined, block 0 logs (event, value, SM clock)
@@ -182,51 +205,58 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool l
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(live ? 16 : 0));
 }
 
-// Resolve the 640 slots of `token` into row buffer `token_count & 1`, list its live chunks and
-// publish both to the other roles. Returns false when a wait gave up.
-__device__ __forceinline__ bool resolve_token(const Params& p, const Shared& sm, int token,
-                                              uint32_t token_count, int tid) {
-  const int lane = tid & 31;
-  const int buffer = token_count & 1;
-  int* rows = sm.rows(buffer);
-  TokenInfo* info = sm.info(buffer);
-  int* scratch = sm.scratch();
-  // The buffer is free once the softmax warps have finished the token that used it two tokens
-  // ago. (Barriers that one role may pass without the others keeping up exist once per buffer:
-  // a phase parity can only tell two consecutive phases apart.)
-  if (token_count >= 2 &&
-      !producer_wait(sm.bar(kTokenDone0 + buffer), ((token_count >> 1) & 1) ^ 1, sm.abort_flag())) return false;
-  const TokenGeometry g = token_geometry(p, token);
-  if (tid == 0) *scratch = kTopK;
-  producer_sync();
-  const int32_t* list = p.indices + (size_t)token * kTopK;
-  {
+// ---- resolver warp ----------------------------------------------------------------------------
+// Runs ahead of everybody else: for each token of this block it resolves the 640 slots into row
+// buffer `token_count & 1`, lists the live chunks and publishes both.
+__device__ void resolver_role(const Params& p, const Shared& sm) {
+  const int lane = threadIdx.x & 31;
+  volatile int* abort_flag = sm.abort_flag();
+  uint32_t token_count = 0;
+  TokenWalk walk(p);
+  for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
+    const int buffer = token_count & 1;
+    int* rows = sm.rows(buffer);
+    TokenInfo* info = sm.info(buffer);
+    // The buffer is free once the softmax warps have finished the token that used it two tokens
+    // ago. (Barriers that one role may pass without the others keeping up exist once per buffer:
+    // a phase parity can only tell two consecutive phases apart.)
+    if (token_count >= 2 &&
+        !warp_wait(sm.bar(kTokenDone0 + buffer), ((token_count >> 1) & 1) ^ 1, abort_flag)) return;
+    const TokenGeometry g = token_geometry(p, token);
+    const int32_t* list = p.indices + (size_t)token * kTopK;
+    int index[kTopK / 32];
     int first = kTopK;
-    for (int rank = tid; rank < kTopK; rank += kProducerThreads)
-      if (__ldg(list + rank) < 0) { first = rank; break; }
-    if (first < kTopK) atomicMin(scratch, first);
-  }
-  producer_sync();
-  const int first_negative = *scratch;
-  for (int slot = tid; slot < kSlots; slot += kProducerThreads)
-    rows[slot] = slot < kWindow
-        ? resolve_window_slot(p, g, token, slot)
-        : resolve_compressed_rank(p, g, token, slot - kWindow, __ldg(list + slot - kWindow), first_negative);
-  producer_sync();
-  if (tid < 32) {  // one warp lists the chunks that hold at least one live slot
-    int count = 0;
-    for (int chunk = 0; chunk < kMaxChunks; ++chunk) {
-      const bool live = rows[chunk * kChunkRows + lane] >= 0 || rows[chunk * kChunkRows + 32 + lane] >= 0;
-      if (__any_sync(0xffffffffu, live)) {
-        if (lane == 0) info->chunk[count] = (unsigned char)chunk;
-        ++count;
-      }
+#pragma unroll
+    for (int i = 0; i < kTopK / 32; ++i) {
+      index[i] = __ldg(list + i * 32 + lane);
+      if (index[i] < 0 && first == kTopK) first = i * 32 + lane;
     }
-    if (lane == 0) { info->token = token; info->chunks = count; }
+    const int first_negative = __reduce_min_sync(0xffffffffu, first);
+    int live_chunks = 0;  // bit c set: chunk c holds a live slot (same in all lanes)
+#pragma unroll
+    for (int i = 0; i < kWindow / 32; ++i) {
+      const int slot = i * 32 + lane;
+      const int row = resolve_window_slot(p, g, token, slot);
+      rows[slot] = row;
+      if (__any_sync(0xffffffffu, row >= 0)) live_chunks |= 1 << (slot / kChunkRows);
+    }
+#pragma unroll
+    for (int i = 0; i < kTopK / 32; ++i) {
+      const int rank = i * 32 + lane;
+      const int row = resolve_compressed_rank(p, g, token, rank, index[i], first_negative);
+      rows[kWindow + rank] = row;
+      if (__any_sync(0xffffffffu, row >= 0)) live_chunks |= 1 << ((kWindow + rank) / kChunkRows);
+    }
+    if (lane == 0) {
+      int count = 0;
+      for (int chunk = 0; chunk < kMaxChunks; ++chunk)
+        if (live_chunks >> chunk & 1) info->chunk[count++] = (unsigned char)chunk;
+      info->token = token;
+      info->chunks = count;
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(sm.bar(kTokenReady0 + buffer));
   }
-  producer_sync();
-  if (lane == 0) mbar_arrive(sm.bar(kTokenReady0 + buffer));
-  return true;
 }
 
 __device__ void producer_role(const Params& p, const Shared& sm) {
@@ -241,13 +271,21 @@ __device__ void producer_role(const Params& p, const Shared& sm) {
   uint32_t ring = 0;  // tiles placed so far (all tokens): a Q tile per working token, then its chunks
   uint32_t occupied = 0, last_is_q = 0, last_parity = 0, next_parity_kv = 0, next_parity_q = 0;
   uint32_t token_count = 0;
-  if (blockIdx.x < p.tokens && !resolve_token(p, sm, blockIdx.x, 0, tid)) return;
-  for (int token = blockIdx.x; token < p.tokens; token += gridDim.x, ++token_count) {
+  int pending = -1;  // stage whose copies are in flight and not yet announced
+  TokenWalk walk(p);
+  for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
+    if (pending >= 0 && !producer_poll(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1)) {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + pending));
+      pending = -1;
+    }
+    if (!producer_wait(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
     const int* rows = sm.rows(token_count & 1);
     const TokenInfo* info = sm.info(token_count & 1);
     const int chunks = info->chunks;
     const char* q = static_cast<const char*>(p.q) + (size_t)token * kHeads * kRowBytes;
-    int pending = -1;  // stage whose copies are in flight and not yet announced
     for (int item = chunks > 0 ? -1 : 0; item < chunks; ++item, ++ring) {
       const uint32_t stage = ring % kStages, bit = 1u << stage;
       const bool is_q = item < 0;
@@ -294,20 +332,12 @@ __device__ void producer_role(const Params& p, const Shared& sm) {
       }
       pending = int(stage);
     }
-    // Resolve the next token while the last copies are in flight.
-    const int next = token + gridDim.x;
-    if (next < p.tokens) {
-      if (tid == 0) TRACE(sm, 1, next);
-      if (!resolve_token(p, sm, next, token_count + 1, tid)) return;
-      if (tid == 0) TRACE(sm, 2, next);
-    }
-    if (pending >= 0) {
-      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-      fence_proxy_async();
-      __syncwarp();
-      if (tid == 0) TRACE(sm, 5, chunks - 1);
-      if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + pending));
-    }
+  }
+  if (pending >= 0) {
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + pending));
   }
 }
 
@@ -357,7 +387,8 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
   // `ring` counts tiles in the shared ring (a Q tile per working token, then its chunks);
   // `chunk_count` counts KV chunks only and selects the S / P buffer.
   uint32_t ring = 0, chunk_count = 0, token_count = 0, working_tokens = 0;
-  for (int token = blockIdx.x; token < p.tokens; token += gridDim.x, ++token_count) {
+  TokenWalk walk(p);
+  for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
     if (!mbar_wait(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
     const int chunks = sm.info(token_count & 1)->chunks;
     if (chunks == 0) continue;
@@ -458,16 +489,17 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
     return true;
   };
 
-  if (blockIdx.x < p.tokens && !prepare(blockIdx.x, 0)) return;
-  for (int token = blockIdx.x; token < p.tokens; token += gridDim.x, ++token_count) {
+  TokenWalk walk(p);
+  if (walk.peek() >= 0 && !prepare(walk.peek(), 0)) return;
+  for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
     const TokenInfo* info = sm.info(token_count & 1);
     const int* rows = sm.rows(token_count & 1);
     const int chunks = info->chunks;
-    const int next = token + gridDim.x;
+    const int next = walk.peek();
     __nv_bfloat16* out = out_base + ((size_t)token * kHeads + head) * kFeatures + half * 256;
     if (chunks == 0) {  // nothing visible: the output row is zero whatever the sink
       for (int i = 0; i < 256; i += 8) *reinterpret_cast<uint4*>(out + i) = make_uint4(0, 0, 0, 0);
-      if (next < p.tokens && !prepare(next, token_count + 1)) return;
+      if (next >= 0 && !prepare(next, token_count + 1)) return;
       __syncwarp();
       if (lane == 0) mbar_arrive(sm.bar(kTokenDone0 + (token_count & 1)));
       continue;
@@ -552,7 +584,7 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
     }
 
     // Next token's Q goes to tensor memory while the last PV of this one runs.
-    if (next < p.tokens && !prepare(next, token_count + 1)) return;
+    if (next >= 0 && !prepare(next, token_count + 1)) return;
 
     // ---- epilogue: O / denominator -> BF16 -> global ------------------------------------------
     while (pv_waited < chunk_count) {
@@ -562,6 +594,10 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
     tc_fence_after_sync();
     if (threadIdx.x == 0) TRACE(sm, 23, token);
     const float inverse = 1.f / run_sum;
+    // 64 columns per pass: tensor memory -> registers -> a swizzled per-warp staging tile ->
+    // global, so that every store instruction writes four complete 128-byte lines.
+    unsigned char* staging = sm.ptr + kSmemStore + warp * 4096;
+    __nv_bfloat16* token_out = out_base + (size_t)token * kHeads * kFeatures;
 #pragma unroll 1
     for (int c = 0; c < 256; c += 64) {
       uint32_t o[64];
@@ -570,14 +606,23 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
         tmem_ld16(tmem + kTmemO + c + q + lane_base, *reinterpret_cast<uint32_t(*)[16]>(&o[q]));
       tmem_wait_ld();
 #pragma unroll
-      for (int q = 0; q < 64; q += 8) {
+      for (int unit = 0; unit < 8; ++unit) {
         uint4 v;
-        v.x = pack_bf16(__uint_as_float(o[q + 0]) * inverse, __uint_as_float(o[q + 1]) * inverse);
-        v.y = pack_bf16(__uint_as_float(o[q + 2]) * inverse, __uint_as_float(o[q + 3]) * inverse);
-        v.z = pack_bf16(__uint_as_float(o[q + 4]) * inverse, __uint_as_float(o[q + 5]) * inverse);
-        v.w = pack_bf16(__uint_as_float(o[q + 6]) * inverse, __uint_as_float(o[q + 7]) * inverse);
-        *reinterpret_cast<uint4*>(out + c + q) = v;
+        v.x = pack_bf16(__uint_as_float(o[unit * 8 + 0]) * inverse, __uint_as_float(o[unit * 8 + 1]) * inverse);
+        v.y = pack_bf16(__uint_as_float(o[unit * 8 + 2]) * inverse, __uint_as_float(o[unit * 8 + 3]) * inverse);
+        v.z = pack_bf16(__uint_as_float(o[unit * 8 + 4]) * inverse, __uint_as_float(o[unit * 8 + 5]) * inverse);
+        v.w = pack_bf16(__uint_as_float(o[unit * 8 + 6]) * inverse, __uint_as_float(o[unit * 8 + 7]) * inverse);
+        *reinterpret_cast<uint4*>(staging + lane * 128 + ((unit ^ (lane & 7)) << 4)) = v;
       }
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = i * 4 + (lane >> 3), unit = lane & 7;  // staging row = owning lane
+        const uint4 v = *reinterpret_cast<const uint4*>(staging + row * 128 + ((unit ^ (row & 7)) << 4));
+        __nv_bfloat16* dst = token_out + (size_t)(warp * 16 + (row & 15)) * kFeatures + (row >> 4) * 256 + c + unit * 8;
+        *reinterpret_cast<uint4*>(dst) = v;
+      }
+      __syncwarp();
     }
     tc_fence_before_sync();
     __syncwarp();
@@ -603,7 +648,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
 
   if (threadIdx.x == 0) {
     const int P = kProducerWarps, S = kSoftmaxWarps;
-    const int counts[kBarCount] = {P, P, S, S, S, 1, P, P, P, 1, 1, 1, 1, 1, S, S, 1, S, S, S, S};
+    const int counts[kBarCount] = {1, 1, S, S, S, 1, P, P, P, 1, 1, 1, 1, 1, S, S, 1, S, S, S, S};
     for (int i = 0; i < kBarCount; ++i) mbar_init(sm.bar(i), counts[i]);
     mbar_fence_init();
     *sm.abort_flag() = 0;
@@ -622,6 +667,8 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
   } else if (warp == kMmaWarp) {
     if ((threadIdx.x & 31) == 0) mma_role(p, sm, tmem);
     __syncwarp();
+  } else if (warp == kResolverWarp) {
+    resolver_role(p, sm);
   } else {
     producer_role(p, sm);
     asm volatile("cp.async.wait_all;\n" ::: "memory");
@@ -652,7 +699,10 @@ inline int launch(const Params& p, cudaStream_t stream, int multiprocessors) {
     configured[device] = true;
   }
   const int grid = p.tokens < multiprocessors ? p.tokens : multiprocessors;
-  attention_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
+  Params launch_params = p;
+  const int per_block = p.tokens / (grid * 4);
+  launch_params.token_group = per_block < 1 ? 1 : (per_block > 8 ? 8 : per_block);
+  attention_kernel<<<grid, kThreads, kSmemBytes, stream>>>(launch_params);
   return int(cudaGetLastError());
 }
 

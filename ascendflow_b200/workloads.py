@@ -24,6 +24,8 @@ CONFIGS = {
     "prefill_q32k_ctx32k": dict(batches=1, queries=32768, context=32768, max_seq=131072),
     "decode_b64_q6_ctx128k": dict(batches=64, queries=6, context=131072, max_seq=131072),
     "decode_b128_q6_ctx128k": dict(batches=128, queries=6, context=131072, max_seq=131072),
+    # A smaller decode case (3.2 GB of caches) sized for multi-pass profiler captures.
+    "decode_b16_q6_ctx128k": dict(batches=16, queries=6, context=131072, max_seq=131072),
 }
 
 
