@@ -66,7 +66,7 @@ constexpr int kSmemBars = kSmemInfo + 2 * 64;               // mbarriers
 constexpr int kSmemMisc = kSmemBars + 32 * 8;               // tmem slot, abort flag
 constexpr int kSmemStore = kSmemMisc + 64;                  // per softmax warp: 32 x 128-byte staging rows
 #ifdef SPARSE_MLA_TRACE
-constexpr int kTraceEntries = 2400;
+constexpr int kTraceEntries = 900;
 constexpr int kSmemTrace = kSmemStore + kSoftmaxWarps * 4096;
 constexpr int kSmemBytes = kSmemTrace + 16 + kTraceEntries * 8 + 1024;
 #else
@@ -159,6 +159,20 @@ __device__ __forceinline__ void trace(const Shared& sm, int event, int value) {
 #define TRACE(sm, event, value) trace(sm, event, value)
 #else
 #define TRACE(sm, event, value) do {} while (0)
+#endif
+
+// Compile-time diagnostic: with SPARSE_MLA_PROFILE defined, one thread per role of block 0 sums
+// the SM clocks it spends in each named section and writes them to `Params::scheduler`.
+#ifdef SPARSE_MLA_PROFILE
+#define PROF_DECL long long prof_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long prof_t_ = 0; (void)prof_t_
+#define PROF_BEGIN prof_t_ = clock64()
+#define PROF_END(i) prof_[i] += clock64() - prof_t_
+#define PROF_FLUSH(p, role) if (blockIdx.x == 0) { long long* o = reinterpret_cast<long long*>((p).scheduler) + (role) * 8; for (int i_ = 0; i_ < 8; ++i_) o[i_] = prof_[i_]; }
+#else
+#define PROF_DECL do {} while (0)
+#define PROF_BEGIN do {} while (0)
+#define PROF_END(i) do {} while (0)
+#define PROF_FLUSH(p, role) do {} while (0)
 #endif
 
 // A producer wait whose outcome is the same for all producer threads: if any of them gave up,
@@ -263,6 +277,8 @@ __device__ void producer_role(const Params& p, const Shared& sm) {
   const int tid = threadIdx.x - kFirstProducerWarp * 32;
   const int lane = tid & 31;
   volatile int* abort_flag = sm.abort_flag();
+  PROF_DECL;
+  const long long prof_start_ = clock64(); (void)prof_start_;
   const char* window_base = static_cast<const char*>(p.ori_kv);
   const char* compressed_base = static_cast<const char*>(p.cmp_kv);
   // Ring bookkeeping. A stage is released either by the MMA warp (a KV tile, kKvFree) or by the
@@ -281,7 +297,9 @@ __device__ void producer_role(const Params& p, const Shared& sm) {
       if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + pending));
       pending = -1;
     }
+    PROF_BEGIN;
     if (!producer_wait(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
+    PROF_END(0);
     const int* rows = sm.rows(token_count & 1);
     const TokenInfo* info = sm.info(token_count & 1);
     const int chunks = info->chunks;
@@ -301,8 +319,11 @@ __device__ void producer_role(const Params& p, const Shared& sm) {
           if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + pending));
           pending = -1;
         }
+        PROF_BEGIN;
         if (!producer_wait(bar, parity, abort_flag)) return;
+        PROF_END(1);
       }
+      PROF_BEGIN;
       occupied |= bit;
       const uint32_t next_parity = is_q ? next_parity_q : next_parity_kv;
       last_parity = (last_parity & ~bit) | (next_parity & bit);
@@ -323,6 +344,8 @@ __device__ void producer_role(const Params& p, const Shared& sm) {
         }
       }
       asm volatile("cp.async.commit_group;\n" ::: "memory");
+      PROF_END(2);
+      PROF_BEGIN;
       if (pending >= 0) {  // the previous tile has landed once at most one group is outstanding
         asm volatile("cp.async.wait_group 1;\n" ::: "memory");
         fence_proxy_async();
@@ -330,6 +353,7 @@ __device__ void producer_role(const Params& p, const Shared& sm) {
         if (tid == 0) TRACE(sm, 5, item - 1);
         if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + pending));
       }
+      PROF_END(3);
       pending = int(stage);
     }
   }
@@ -339,6 +363,10 @@ __device__ void producer_role(const Params& p, const Shared& sm) {
     __syncwarp();
     if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + pending));
   }
+#ifdef SPARSE_MLA_PROFILE
+  prof_[7] = clock64() - prof_start_;
+#endif
+  if (tid == 0) { PROF_FLUSH(p, 2); }
 }
 
 // ---- MMA warp (one thread) --------------------------------------------------------------------
@@ -384,22 +412,32 @@ __device__ __forceinline__ void issue_pv(const Shared& sm, uint32_t tmem, int st
 
 __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
   volatile int* abort_flag = sm.abort_flag();
+  PROF_DECL;
+  const long long prof_start_ = clock64(); (void)prof_start_;
   // `ring` counts tiles in the shared ring (a Q tile per working token, then its chunks);
   // `chunk_count` counts KV chunks only and selects the S / P buffer.
   uint32_t ring = 0, chunk_count = 0, token_count = 0, working_tokens = 0;
   TokenWalk walk(p);
   for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
+    PROF_BEGIN;
     if (!mbar_wait(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
+    PROF_END(0);
     const int chunks = sm.info(token_count & 1)->chunks;
     if (chunks == 0) continue;
     ++ring;  // the token's Q tile: consumed by the softmax warps
+    PROF_BEGIN;
     if (!mbar_wait(sm.bar(kQFull), working_tokens & 1, abort_flag)) return;
+    PROF_END(1);
     {  // first QK of the token
       const uint32_t stage = ring % kStages, use = ring / kStages;
+      PROF_BEGIN;
       if (!mbar_wait(sm.bar(kKvFull0 + stage), use & 1, abort_flag)) return;
+      PROF_END(2);
       tc_fence_after_sync();
       TRACE(sm, 13, 0);
+      PROF_BEGIN;
       issue_qk(sm, tmem, stage, chunk_count & 1);
+      PROF_END(3);
       mma_commit(sm.bar(kSFull0 + (chunk_count & 1)));
       if (chunks == 1) mma_commit(sm.bar(kQFree));
       TRACE(sm, 14, 0);
@@ -407,30 +445,44 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
     for (int i = 0; i < chunks; ++i, ++chunk_count, ++ring) {
       if (i + 1 < chunks) {  // QK of the next chunk runs while the softmax warps work on this one
         const uint32_t n = ring + 1, stage = n % kStages, use = n / kStages, c = chunk_count + 1;
+        PROF_BEGIN;
         if (!mbar_wait(sm.bar(kKvFull0 + stage), use & 1, abort_flag)) return;
+        PROF_END(2);
         tc_fence_after_sync();
         TRACE(sm, 13, i + 1);
+        PROF_BEGIN;
         // The S buffer it overwrites held P of chunk c - 2, whose PV was issued before: in order.
         issue_qk(sm, tmem, stage, c & 1);
+        PROF_END(3);
         mma_commit(sm.bar(kSFull0 + (c & 1)));
         if (i + 2 == chunks) mma_commit(sm.bar(kQFree));
         TRACE(sm, 14, i + 1);
       }
       const uint32_t stage = ring % kStages, c = chunk_count;
       if (i == 0) {  // the previous token's epilogue must have read O
+        PROF_BEGIN;
         if (!mbar_wait(sm.bar(kOFree), (working_tokens & 1) ^ 1, abort_flag)) return;
+        PROF_END(4);
       }
       TRACE(sm, 10, i);
+      PROF_BEGIN;
       if (!mbar_wait(sm.bar(kPFull0 + (c & 1)), (c >> 1) & 1, abort_flag)) return;
+      PROF_END(5);
       tc_fence_after_sync();
       TRACE(sm, 11, i);
+      PROF_BEGIN;
       issue_pv(sm, tmem, stage, c & 1, i > 0);
+      PROF_END(6);
       mma_commit(sm.bar(kKvFree0 + stage));
       mma_commit(sm.bar(kODone));
       TRACE(sm, 12, i);
     }
     ++working_tokens;
   }
+#ifdef SPARSE_MLA_PROFILE
+  prof_[7] = clock64() - prof_start_;
+#endif
+  PROF_FLUSH(p, 0);
 }
 
 // ---- softmax / correction / epilogue warps ----------------------------------------------------
@@ -464,6 +516,8 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   const int head = warp * 16 + (lane & 15);
   const uint32_t lane_base = uint32_t(warp * 32) << 16;
   volatile int* abort_flag = sm.abort_flag();
+  PROF_DECL;
+  const long long prof_start_ = clock64(); (void)prof_start_;
   const float sink = __ldg(p.sinks + head) * 1.4426950408889634f;  // log2 domain
   uint32_t ring = 0, chunk_count = 0, token_count = 0, pv_waited = 0, q_loads = 0;
   __nv_bfloat16* out_base = static_cast<__nv_bfloat16*>(p.out);
@@ -513,7 +567,10 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       const uint32_t s_addr = tmem + kTmemS + buffer * 64 + lane_base;
 
       if (threadIdx.x == 0) TRACE(sm, 20, i);
+      PROF_BEGIN;
       if (!warp_wait(sm.bar(kSFull0 + buffer), (chunk_count >> 1) & 1, abort_flag)) return;
+      PROF_END(0);
+      PROF_BEGIN;
       if (threadIdx.x == 0) TRACE(sm, 21, i);
       tc_fence_after_sync();
       float s[64];
@@ -579,12 +636,16 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
         ++pv_waited;
       }
       __syncwarp();
+      PROF_END(1);
       if (threadIdx.x == 0) TRACE(sm, 22, i);
       if (lane == 0) mbar_arrive(sm.bar(kPFull0 + buffer));
     }
 
     // Next token's Q goes to tensor memory while the last PV of this one runs.
+    PROF_BEGIN;
     if (next >= 0 && !prepare(next, token_count + 1)) return;
+    PROF_END(2);
+    PROF_BEGIN;
 
     // ---- epilogue: O / denominator -> BF16 -> global ------------------------------------------
     while (pv_waited < chunk_count) {
@@ -592,6 +653,8 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       ++pv_waited;
     }
     tc_fence_after_sync();
+    PROF_END(3);
+    PROF_BEGIN;
     if (threadIdx.x == 0) TRACE(sm, 23, token);
     const float inverse = 1.f / run_sum;
     // 64 columns per pass: tensor memory -> registers -> a swizzled per-warp staging tile ->
@@ -626,12 +689,17 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
     }
     tc_fence_before_sync();
     __syncwarp();
+    PROF_END(4);
     if (threadIdx.x == 0) TRACE(sm, 24, token);
     if (lane == 0) {
       mbar_arrive(sm.bar(kOFree));
       mbar_arrive(sm.bar(kTokenDone0 + (token_count & 1)));
     }
   }
+#ifdef SPARSE_MLA_PROFILE
+  prof_[7] = clock64() - prof_start_;
+#endif
+  if (threadIdx.x == 0) { PROF_FLUSH(p, 1); }
 }
 
 // ---- kernel and launch ------------------------------------------------------------------------

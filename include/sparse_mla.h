@@ -114,6 +114,19 @@ int launch_sparse_mla_f16(void* stream, void* arg_q, void* arg_ori_kv, void* arg
                           void* arg_attention_out, void* npu_workspace, int64_t B, int64_t T,
                           int64_t PAGES, int64_t ORI_BLOCKS, int64_t CMP_BLOCKS, int64_t CMP_PAGE);
 
+/* ---- BF16 cross-check kernel: the same operator on the warp-level tensor instructions
+ * (ldmatrix + mma.sync) instead of tcgen05. Same arguments and contract as launch_sparse_mla.
+ * It has no counterpart in the reference; tests compare the two implementations on full-size
+ * inputs where the CPU oracle can only afford a sample. */
+int launch_sparse_mla_warp_mma(void* stream, void* arg_q, void* arg_ori_kv, void* arg_cmp_kv,
+                               void* arg_cmp_sparse_indices, void* arg_ori_block_table,
+                               void* arg_cmp_block_table, void* arg_cu_seqlens_q,
+                               void* arg_seqused_ori_kv, void* arg_seqused_cmp_kv,
+                               void* arg_cmp_residual_kv, void* arg_ori_topk_length,
+                               void* arg_sinks, void* arg_attention_out, void* npu_workspace,
+                               int64_t B, int64_t T, int64_t PAGES, int64_t ORI_BLOCKS,
+                               int64_t CMP_BLOCKS, int64_t CMP_PAGE);
+
 /* ---- Gathered index set export -------------------------------------------------------------
  * Writes, for every token and slot 0..639, the physical cache row the attention kernel gathers
  * (a row of ori_kv viewed as [ORI_BLOCKS*128, 512] for slots < 128, a row of cmp_kv viewed as
