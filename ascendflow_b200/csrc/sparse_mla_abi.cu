@@ -133,6 +133,31 @@ int clear_workspace(cudaStream_t stream, void* workspace) {
   return int(cudaMemsetAsync(workspace, 0, kWorkspaceBytes, stream));
 }
 
+// Scratch of the entry point that allocates nothing: the workspace of one attention launch
+// (status block + scheduler words) as a file-scope device array. Every GPU that loads this
+// library holds these bytes until the process exits. In host code the name below is only a
+// host-side stand-in for the device array, never a device address: the address a kernel can use
+// comes from cudaGetSymbolAddress, once per device, with that device current.
+constexpr size_t kStaticWorkspaceBytes = 1024;
+static __device__ __align__(256) unsigned char static_workspace[kStaticWorkspaceBytes];
+
+// Device address of `static_workspace` on the current device; nullptr (and *error set) on failure.
+void* static_workspace_address(int* error) {
+  static void* cached[64] = {nullptr};
+  int device = 0;
+  cudaError_t status = cudaGetDevice(&device);
+  if (status != cudaSuccess) { *error = int(status); return nullptr; }
+  if (device < 0 || device >= 64) { *error = -1; return nullptr; }
+  if (cached[device] == nullptr) {
+    void* address = nullptr;
+    status = cudaGetSymbolAddress(&address, static_workspace);
+    if (status != cudaSuccess || address == nullptr) { *error = status != cudaSuccess ? int(status) : -1; return nullptr; }
+    cached[device] = address;
+  }
+  *error = 0;
+  return cached[device];
+}
+
 }  // namespace
 }  // namespace sparse_mla
 
@@ -239,6 +264,32 @@ int launch_sparse_mla_resolve_rows(void* stream, void* arg_cmp_sparse_indices,
   const int64_t cap = int64_t(multiprocessors()) * 8;
   resolve_rows_kernel<<<int(T < cap ? T : cap), 128, 0, s>>>(p, static_cast<int32_t*>(arg_resolved_rows));
   return int(cudaGetLastError());
+}
+
+int launch_sparse_mla_static_workspace(void* stream, void* arg_q, void* arg_ori_kv, void* arg_cmp_kv,
+                                       void* arg_cmp_sparse_indices, void* arg_ori_block_table,
+                                       void* arg_cmp_block_table, void* arg_cu_seqlens_q,
+                                       void* arg_seqused_ori_kv, void* arg_seqused_cmp_kv,
+                                       void* arg_cmp_residual_kv, void* arg_ori_topk_length,
+                                       void* arg_sinks, void* arg_attention_out, int64_t B, int64_t T,
+                                       int64_t PAGES, int64_t ORI_BLOCKS, int64_t CMP_BLOCKS,
+                                       int64_t CMP_PAGE) {
+  uint64_t needed = 0;
+  if (workspace_size(&needed, B, T, PAGES, ORI_BLOCKS, CMP_BLOCKS, CMP_PAGE) != 0) return -1;
+  if (needed > kStaticWorkspaceBytes) return SPARSE_MLA_STATIC_WORKSPACE_TOO_SMALL;
+  int error = 0;
+  void* workspace = static_workspace_address(&error);  // first call on a device: symbol look-up
+  if (workspace == nullptr) return error;
+  Params p;
+  if (!fill(p, arg_q, arg_ori_kv, arg_cmp_kv, arg_cmp_sparse_indices, arg_ori_block_table,
+            arg_cmp_block_table, arg_cu_seqlens_q, arg_seqused_ori_kv, arg_seqused_cmp_kv,
+            arg_cmp_residual_kv, arg_ori_topk_length, arg_sinks, arg_attention_out, workspace,
+            B, T, PAGES, ORI_BLOCKS, CMP_BLOCKS, CMP_PAGE))
+    return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left: the status block must start at zero.
+  if (int status = int(cudaMemsetAsync(workspace, 0, kStaticWorkspaceBytes, s))) return status;
+  return umma::launch(p, s, multiprocessors());
 }
 
 int read_status_sparse_mla(void* stream, void* npu_workspace, int32_t* host_words) {

@@ -143,6 +143,35 @@ int launch_sparse_mla_resolve_rows(void* stream, void* arg_cmp_sparse_indices,
                                    void* npu_workspace, int64_t B, int64_t T, int64_t PAGES,
                                    int64_t ORI_BLOCKS, int64_t CMP_BLOCKS, int64_t CMP_PAGE);
 
+/* ---- Attention launch that allocates nothing ---------------------------------------------------
+ * No counterpart in the reference (its runtime always owns a malloc'ed workspace arena,
+ * src/runtime/kernel.py:39-49). Same operator, kernel and tensor contract as launch_sparse_mla,
+ * for callers that must not or cannot allocate device memory around the call: code running
+ * under an allocator freeze (inside a serving engine's memory-planned step, a plugin whose
+ * host hands it a fixed arena, a process that has already given the whole GPU to a pool) and
+ * has no workspace to pass. The workspace lives in a static device array inside this library
+ * instead: SPARSE_MLA_STATIC_WORKSPACE_BYTES per GPU, held from library load until the
+ * process exits.
+ *  - The function calls no cudaMalloc / cudaFree and no allocating library routine.
+ *  - The first call on each device looks the array's device address up (cudaGetSymbolAddress);
+ *    make that first call outside any stream capture.
+ *  - Sizes whose workspace would exceed the array are refused with
+ *    SPARSE_MLA_STATIC_WORKSPACE_TOO_SMALL (today every legal size needs 1024 bytes and fits);
+ *    invalid sizes return -1 as in launch_sparse_mla.
+ *  - All calls on a device share the one array. It is cleared on the stream before each launch,
+ *    so calls on the same stream are safe back to back; calls that overlap on the GPU
+ *    (different streams, different threads) race on it and must not be made. */
+#define SPARSE_MLA_STATIC_WORKSPACE_BYTES 1024
+#define SPARSE_MLA_STATIC_WORKSPACE_TOO_SMALL (-2)
+int launch_sparse_mla_static_workspace(void* stream, void* arg_q, void* arg_ori_kv, void* arg_cmp_kv,
+                                       void* arg_cmp_sparse_indices, void* arg_ori_block_table,
+                                       void* arg_cmp_block_table, void* arg_cu_seqlens_q,
+                                       void* arg_seqused_ori_kv, void* arg_seqused_cmp_kv,
+                                       void* arg_cmp_residual_kv, void* arg_ori_topk_length,
+                                       void* arg_sinks, void* arg_attention_out, int64_t B, int64_t T,
+                                       int64_t PAGES, int64_t ORI_BLOCKS, int64_t CMP_BLOCKS,
+                                       int64_t CMP_PAGE);
+
 /* Copies the status block of a workspace to `host_words` (host, SPARSE_MLA_STATUS_WORDS int32)
  * after synchronising `stream`. word 0: a SPARSE_MLA_STATUS_* code, word 1: token, word 2: detail. */
 int read_status_sparse_mla(void* stream, void* npu_workspace, int32_t* host_words);
