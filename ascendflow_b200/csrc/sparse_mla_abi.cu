@@ -195,7 +195,7 @@ int launch_sparse_mla(void* stream, void* arg_q, void* arg_ori_kv, void* arg_cmp
     return -1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int status = clear_workspace(s, npu_workspace)) return status;
-  return umma::launch(p, s, multiprocessors());
+  return umma::launch<1>(p, s, multiprocessors());
 }
 
 int launch_sparse_mla_f16(void* stream, void* arg_q, void* arg_ori_kv, void* arg_cmp_kv,
@@ -212,13 +212,8 @@ int launch_sparse_mla_f16(void* stream, void* arg_q, void* arg_ori_kv, void* arg
             B, T, PAGES, ORI_BLOCKS, CMP_BLOCKS, CMP_PAGE))
     return -1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  static bool configured = false;
-  if (int status = configure_once(warp_mma::attention_kernel<__half>, warp_mma::kSmemBytes, configured))
-    return status;
   if (int status = clear_workspace(s, npu_workspace)) return status;
-  const int grid = int(T < int64_t(multiprocessors()) ? T : multiprocessors());
-  warp_mma::attention_kernel<__half><<<grid, warp_mma::kThreads, warp_mma::kSmemBytes, s>>>(p);
-  return int(cudaGetLastError());
+  return umma::launch<0>(p, s, multiprocessors());
 }
 
 // The portable-instruction BF16 kernel under its own name: the cross-check of the tcgen05 kernel.
@@ -289,7 +284,7 @@ int launch_sparse_mla_static_workspace(void* stream, void* arg_q, void* arg_ori_
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // The array keeps whatever the previous call left: the status block must start at zero.
   if (int status = int(cudaMemsetAsync(workspace, 0, kStaticWorkspaceBytes, s))) return status;
-  return umma::launch(p, s, multiprocessors());
+  return umma::launch<1>(p, s, multiprocessors());
 }
 
 int read_status_sparse_mla(void* stream, void* npu_workspace, int32_t* host_words) {

@@ -1,5 +1,6 @@
 // Sparse MLA attention on the Blackwell tensor path: tcgen05.mma with operands and accumulators
-// in tensor memory, warp-specialised and software-pipelined. BF16 storage, FP32 accumulation.
+// in tensor memory, warp-specialised and software-pipelined. BF16 or FP16 storage (template
+// parameter kFormat), FP32 accumulation.
 //
 // One persistent block per SM owns one query token at a time (64 heads x 512 features) and
 // walks the token's live 64-row chunks (window rows first, then the compressed ranks in list
@@ -35,6 +36,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "sparse_mla_common.cuh"
 #include "tcgen05_ptx.cuh"
@@ -91,8 +93,9 @@ enum Bar {
   kSFull0, kSFull1, kPFull0, kPFull1, kODone, kOFree, kQStageFree0, kQStageFree1, kQStageFree2, kBarCount
 };
 
-constexpr uint32_t kIdescQK = idesc_f16(64, 64, 1, 0, 0);
-constexpr uint32_t kIdescPV = idesc_f16(64, 256, 1, 0, 1);
+// Storage formats of kind::f16 instructions: 0 = IEEE half, 1 = BF16.
+template <int kFormat> constexpr uint32_t kIdescQK = idesc_f16(64, 64, kFormat, 0, 0);
+template <int kFormat> constexpr uint32_t kIdescPV = idesc_f16(64, 256, kFormat, 0, 1);
 
 // Byte offset of 16-byte unit `unit` (0..63) of row `row` in a K-major 128-byte-swizzled tile
 // of 64 rows: eight 64-feature blocks of [64 rows x 128 bytes].
@@ -373,43 +376,46 @@ __device__ void producer_role(const Params& p, const Shared& sm) {
 
 // Compile-time unrolled issue loops: every operand offset and accumulate flag is an immediate,
 // so the issuing thread spends a couple of instructions per MMA and stays ahead of the pipe.
-template <int K>
+template <int kFormat, int K>
 __device__ __forceinline__ void issue_qk_steps(uint32_t s_tmem, uint32_t q_tmem, uint64_t x_desc) {
   if constexpr (K < kFeatures / 16) {
     constexpr uint32_t half = (K >> 4) * kHalfLanes;
     constexpr uint32_t offset = (K >> 2) * kBlockBytes + (K & 3) * 32;
-    mma_ts_c<(K & 15) != 0>(s_tmem + half, q_tmem + (K & 15) * 8 + half, x_desc + (offset >> 4), kIdescQK);
-    issue_qk_steps<K + 1>(s_tmem, q_tmem, x_desc);
+    mma_ts_c<(K & 15) != 0>(s_tmem + half, q_tmem + (K & 15) * 8 + half, x_desc + (offset >> 4), kIdescQK<kFormat>);
+    issue_qk_steps<kFormat, K + 1>(s_tmem, q_tmem, x_desc);
   }
 }
 
 // S[buffer] = Q X^T for one 64-row tile, as two partial products: features 0-255 in lane half 0,
 // 256-511 in lane half 1. A = Q from tensor memory (8 columns of BF16 pairs per K=16 step).
+template <int kFormat>
 __device__ __forceinline__ void issue_qk(const Shared& sm, uint32_t tmem, int stage, int buffer) {
   const uint64_t x_desc = smem_desc_sw128(sm.base + kSmemKv + stage * kTileBytes, 16, 1024);
-  issue_qk_steps<0>(tmem + kTmemS + buffer * 64, tmem + kTmemQ, x_desc);
+  issue_qk_steps<kFormat, 0>(tmem + kTmemS + buffer * 64, tmem + kTmemQ, x_desc);
 }
 
-template <int I, bool kFirst>
+template <int kFormat, int I, bool kFirst>
 __device__ __forceinline__ void issue_pv_steps(uint32_t o_tmem, uint32_t p_tmem, uint64_t x_desc) {
   if constexpr (I < 2 * (kChunkRows / 16)) {
     constexpr int h = I / (kChunkRows / 16), k = I % (kChunkRows / 16);
     constexpr uint32_t half = h * kHalfLanes;
     constexpr uint32_t offset = h * 4 * kBlockBytes + k * 2048;
-    mma_ts_c<!(kFirst && k == 0)>(o_tmem + half, p_tmem + k * 8 + half, x_desc + (offset >> 4), kIdescPV);
-    issue_pv_steps<I + 1, kFirst>(o_tmem, p_tmem, x_desc);
+    mma_ts_c<!(kFirst && k == 0)>(o_tmem + half, p_tmem + k * 8 + half, x_desc + (offset >> 4), kIdescPV<kFormat>);
+    issue_pv_steps<kFormat, I + 1, kFirst>(o_tmem, p_tmem, x_desc);
   }
 }
 
 // O += P X for one 64-row tile: features 0-255 in lane half 0, 256-511 in lane half 1.
 // A = P from tensor memory (written to both halves by the softmax threads); B = X with features
 // contiguous: four 64-feature blocks kBlockBytes apart, 8-row groups 1024 bytes apart.
+template <int kFormat>
 __device__ __forceinline__ void issue_pv(const Shared& sm, uint32_t tmem, int stage, int buffer, bool accumulate) {
   const uint64_t x_desc = smem_desc_sw128(sm.base + kSmemKv + stage * kTileBytes, kBlockBytes, 1024);
-  if (accumulate) issue_pv_steps<0, false>(tmem + kTmemO, tmem + kTmemS + buffer * 64, x_desc);
-  else issue_pv_steps<0, true>(tmem + kTmemO, tmem + kTmemS + buffer * 64, x_desc);
+  if (accumulate) issue_pv_steps<kFormat, 0, false>(tmem + kTmemO, tmem + kTmemS + buffer * 64, x_desc);
+  else issue_pv_steps<kFormat, 0, true>(tmem + kTmemO, tmem + kTmemS + buffer * 64, x_desc);
 }
 
+template <int kFormat>
 __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
   volatile int* abort_flag = sm.abort_flag();
   PROF_DECL;
@@ -436,7 +442,7 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
       tc_fence_after_sync();
       TRACE(sm, 13, 0);
       PROF_BEGIN;
-      issue_qk(sm, tmem, stage, chunk_count & 1);
+      issue_qk<kFormat>(sm, tmem, stage, chunk_count & 1);
       PROF_END(3);
       mma_commit(sm.bar(kSFull0 + (chunk_count & 1)));
       if (chunks == 1) mma_commit(sm.bar(kQFree));
@@ -452,7 +458,7 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
         TRACE(sm, 13, i + 1);
         PROF_BEGIN;
         // The S buffer it overwrites held P of chunk c - 2, whose PV was issued before: in order.
-        issue_qk(sm, tmem, stage, c & 1);
+        issue_qk<kFormat>(sm, tmem, stage, c & 1);
         PROF_END(3);
         mma_commit(sm.bar(kSFull0 + (c & 1)));
         if (i + 2 == chunks) mma_commit(sm.bar(kQFree));
@@ -471,7 +477,7 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
       tc_fence_after_sync();
       TRACE(sm, 11, i);
       PROF_BEGIN;
-      issue_pv(sm, tmem, stage, c & 1, i > 0);
+      issue_pv<kFormat>(sm, tmem, stage, c & 1, i > 0);
       PROF_END(6);
       mma_commit(sm.bar(kKvFree0 + stage));
       mma_commit(sm.bar(kODone));
@@ -487,9 +493,15 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
 
 // ---- softmax / correction / epilogue warps ----------------------------------------------------
 
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&v);
+template <int kFormat>
+__device__ __forceinline__ uint32_t pack_pair(float a, float b) {  // two FP32 -> two storage words
+  if constexpr (kFormat == 1) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
 }
 
 // Copy this thread's half row of Q (256 BF16 = 128 words) from a staged shared tile (same
@@ -510,6 +522,7 @@ __device__ __forceinline__ void load_q_half_row(const Shared& sm, uint32_t tmem_
   tmem_wait_st();
 }
 
+template <int kFormat>
 __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int half = lane >> 4;
@@ -624,7 +637,7 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       for (int c = 0; c < 2; ++c) {
         uint32_t packed[16];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) packed[e] = pack_bf16(s[c * 32 + 2 * e], s[c * 32 + 2 * e + 1]);
+        for (int e = 0; e < 16; ++e) packed[e] = pack_pair<kFormat>(s[c * 32 + 2 * e], s[c * 32 + 2 * e + 1]);
         tmem_st16(s_addr + c * 16, packed);
       }
       tmem_wait_st();
@@ -671,10 +684,10 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
 #pragma unroll
       for (int unit = 0; unit < 8; ++unit) {
         uint4 v;
-        v.x = pack_bf16(__uint_as_float(o[unit * 8 + 0]) * inverse, __uint_as_float(o[unit * 8 + 1]) * inverse);
-        v.y = pack_bf16(__uint_as_float(o[unit * 8 + 2]) * inverse, __uint_as_float(o[unit * 8 + 3]) * inverse);
-        v.z = pack_bf16(__uint_as_float(o[unit * 8 + 4]) * inverse, __uint_as_float(o[unit * 8 + 5]) * inverse);
-        v.w = pack_bf16(__uint_as_float(o[unit * 8 + 6]) * inverse, __uint_as_float(o[unit * 8 + 7]) * inverse);
+        v.x = pack_pair<kFormat>(__uint_as_float(o[unit * 8 + 0]) * inverse, __uint_as_float(o[unit * 8 + 1]) * inverse);
+        v.y = pack_pair<kFormat>(__uint_as_float(o[unit * 8 + 2]) * inverse, __uint_as_float(o[unit * 8 + 3]) * inverse);
+        v.z = pack_pair<kFormat>(__uint_as_float(o[unit * 8 + 4]) * inverse, __uint_as_float(o[unit * 8 + 5]) * inverse);
+        v.w = pack_pair<kFormat>(__uint_as_float(o[unit * 8 + 6]) * inverse, __uint_as_float(o[unit * 8 + 7]) * inverse);
         *reinterpret_cast<uint4*>(staging + lane * 128 + ((unit ^ (lane & 7)) << 4)) = v;
       }
       __syncwarp();
@@ -704,6 +717,7 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
 
 // ---- kernel and launch ------------------------------------------------------------------------
 
+template <int kFormat>
 __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) {
   extern __shared__ unsigned char smem_raw[];
   Shared sm;
@@ -731,9 +745,9 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
   const uint32_t tmem = *tmem_slot;
 
   if (warp < kSoftmaxWarps) {
-    softmax_role(p, sm, tmem);
+    softmax_role<kFormat>(p, sm, tmem);
   } else if (warp == kMmaWarp) {
-    if ((threadIdx.x & 31) == 0) mma_role(p, sm, tmem);
+    if ((threadIdx.x & 31) == 0) mma_role<kFormat>(p, sm, tmem);
     __syncwarp();
   } else if (warp == kResolverWarp) {
     resolver_role(p, sm);
@@ -755,6 +769,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
 #endif
 }
 
+template <int kFormat>
 inline int launch(const Params& p, cudaStream_t stream, int multiprocessors) {
   static bool configured[64] = {false};
   int device = 0;
@@ -762,7 +777,7 @@ inline int launch(const Params& p, cudaStream_t stream, int multiprocessors) {
   if (error != cudaSuccess) return int(error);
   if (device < 0 || device >= 64) return -1;
   if (!configured[device]) {
-    error = cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    error = cudaFuncSetAttribute(attention_kernel<kFormat>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (error != cudaSuccess) return int(error);
     configured[device] = true;
   }
@@ -770,7 +785,7 @@ inline int launch(const Params& p, cudaStream_t stream, int multiprocessors) {
   Params launch_params = p;
   const int per_block = p.tokens / (grid * 4);
   launch_params.token_group = per_block < 1 ? 1 : (per_block > 8 ? 8 : per_block);
-  attention_kernel<<<grid, kThreads, kSmemBytes, stream>>>(launch_params);
+  attention_kernel<kFormat><<<grid, kThreads, kSmemBytes, stream>>>(launch_params);
   return int(cudaGetLastError());
 }
 

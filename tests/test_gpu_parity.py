@@ -152,3 +152,26 @@ def test_status_block_reports_a_bad_page_without_faulting(ops):
     actual = S.output_to_numpy(tensors["attention_out"], "bf16")
     assert np.isfinite(actual).all()
     torch.cuda.synchronize()
+
+
+def test_upstream_shaped_entry(ops):
+    import torch
+
+    from ascendflow_b200.diagnostics import CompileError
+    from ascendflow_b200.upstream import sparse_flash_mla
+
+    policy = default_policy()
+    data = O.validation_inputs(policy, "mixed")
+    tensors, _ = S.to_device(data, policy)
+    names = ("q", "ori_kv", "cmp_kv", "cmp_sparse_indices", "ori_block_table", "cmp_block_table",
+             "cu_seqlens_q", "seqused_ori_kv", "seqused_cmp_kv", "cmp_residual_kv", "ori_topk_length", "sinks")
+    out = sparse_flash_mla(*(tensors[n] for n in names), softmax_scale=512 ** -0.5, cmp_ratio=2)
+    S.assert_close(S.output_to_numpy(out, "bf16"), O.reference_fp32_from_data(data, policy), "upstream entry")
+    # No sink given: the denominator is the plain softmax sum.
+    free = sparse_flash_mla(*(tensors[n] for n in names[:10]))
+    data["sinks"] = np.full(64, -1.0e30, dtype=np.float32)
+    S.assert_close(S.output_to_numpy(free, "bf16"), O.reference_fp32_from_data(data, policy), "no sink")
+    with pytest.raises(CompileError, match="LSE"):
+        sparse_flash_mla(*(tensors[n] for n in names), return_softmax_lse=True)
+    with pytest.raises(CompileError, match="TND"):
+        sparse_flash_mla(*(tensors[n] for n in names), layout_q="BSND")
