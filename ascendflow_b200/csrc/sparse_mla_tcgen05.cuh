@@ -222,13 +222,44 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool l
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(live ? 16 : 0));
 }
 
+// Warp-cooperative form of `token_geometry`: the request search probes 32 positions of
+// cu_seqlens_q per step instead of one, and every other per-token scalar is loaded before the
+// search so that the loads overlap (a cold block starts with this chain on its critical path).
+__device__ __forceinline__ TokenGeometry token_geometry_warp(const Params& p, int token, int lane) {
+  const int requested = __ldg(p.topk_len + token);
+  int lo = 0, hi = p.batches;  // invariant: cu[lo] <= token < cu[hi]
+  while (hi - lo > 1) {
+    const int step = (hi - lo + 31) >> 5;
+    const int probe = lo + lane * step;
+    const bool below = probe < hi && __ldg(p.cu + probe) <= token;
+    const unsigned mask = __ballot_sync(0xffffffffu, below);  // lane 0 probes cu[lo]: always set
+    const int last = 31 - __clz(mask);
+    lo += last * step;
+    hi = min(hi, lo + step);
+  }
+  TokenGeometry g;
+  g.batch = lo;
+  const int begin = __ldg(p.cu + lo), end = __ldg(p.cu + lo + 1);
+  const int length = __ldg(p.seq_ori + lo), available = __ldg(p.seq_cmp + lo), residual = __ldg(p.residual + lo);
+  const int count = end - begin, offset = token - begin;
+  g.right = max(0, length - count + offset + 1);
+  g.visible = min(kWindow, g.right);
+  if (requested > 0) g.visible = min(g.visible, requested);
+  g.cutoff = max(0, available * p.ratio + residual - count + offset + 1) / p.ratio;
+  g.bound = min(min(kTopK, available), g.cutoff);
+  return g;
+}
+
 // ---- resolver warp ----------------------------------------------------------------------------
 // Runs ahead of everybody else: for each token of this block it resolves the 640 slots into row
 // buffer `token_count & 1`, lists the live chunks and publishes both.
 __device__ void resolver_role(const Params& p, const Shared& sm) {
   const int lane = threadIdx.x & 31;
   volatile int* abort_flag = sm.abort_flag();
+  PROF_DECL;
+  const long long prof_start_ = clock64(); (void)prof_start_;
   uint32_t token_count = 0;
+  PROF_BEGIN;
   TokenWalk walk(p);
   for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
     const int buffer = token_count & 1;
@@ -239,30 +270,63 @@ __device__ void resolver_role(const Params& p, const Shared& sm) {
     // a phase parity can only tell two consecutive phases apart.)
     if (token_count >= 2 &&
         !warp_wait(sm.bar(kTokenDone0 + buffer), ((token_count >> 1) & 1) ^ 1, abort_flag)) return;
-    const TokenGeometry g = token_geometry(p, token);
+    PROF_END(0);  // since the previous token's publication (or role start): waiting for a free buffer
+    PROF_BEGIN;
+    // The index list does not depend on the geometry: its loads go out first.
     const int32_t* list = p.indices + (size_t)token * kTopK;
     int index[kTopK / 32];
+#pragma unroll
+    for (int i = 0; i < kTopK / 32; ++i) index[i] = __ldg(list + i * 32 + lane);
+    const TokenGeometry g = token_geometry_warp(p, token, lane);
+    PROF_END(1);
+    PROF_BEGIN;
     int first = kTopK;
 #pragma unroll
-    for (int i = 0; i < kTopK / 32; ++i) {
-      index[i] = __ldg(list + i * 32 + lane);
+    for (int i = 0; i < kTopK / 32; ++i)
       if (index[i] < 0 && first == kTopK) first = i * 32 + lane;
-    }
     const int first_negative = __reduce_min_sync(0xffffffffu, first);
-    int live_chunks = 0;  // bit c set: chunk c holds a live slot (same in all lanes)
+    PROF_END(2);
+    PROF_BEGIN;
+    // Same selection as resolve_window_slot / resolve_compressed_rank, in three passes so that
+    // all block-table loads are in flight together (a branch or vote between them would
+    // serialise twenty dependent round trips to memory): columns, loads, rows.
+    int resolved[kSlots / 32], column[kSlots / 32], within[kSlots / 32];
 #pragma unroll
     for (int i = 0; i < kWindow / 32; ++i) {
       const int slot = i * 32 + lane;
-      const int row = resolve_window_slot(p, g, token, slot);
-      rows[slot] = row;
-      if (__any_sync(0xffffffffu, row >= 0)) live_chunks |= 1 << (slot / kChunkRows);
+      const int position = g.right - g.visible + slot;
+      const bool live = slot < g.visible;
+      column[i] = live ? position / kPage : -1;
+      within[i] = position % kPage;
     }
 #pragma unroll
     for (int i = 0; i < kTopK / 32; ++i) {
       const int rank = i * 32 + lane;
-      const int row = resolve_compressed_rank(p, g, token, rank, index[i], first_negative);
-      rows[kWindow + rank] = row;
-      if (__any_sync(0xffffffffu, row >= 0)) live_chunks |= 1 << ((kWindow + rank) / kChunkRows);
+      const bool live = rank < g.bound && rank < first_negative && index[i] < g.cutoff;
+      column[kWindow / 32 + i] = live ? index[i] / p.cmp_page : -1;
+      within[kWindow / 32 + i] = index[i] % p.cmp_page;
+    }
+#pragma unroll
+    for (int i = 0; i < kSlots / 32; ++i) {
+      const int32_t* table = (i < kWindow / 32 ? p.ori_table : p.cmp_table) + (size_t)g.batch * p.pages;
+      resolved[i] = __ldg(table + min(max(column[i], 0), p.pages - 1));  // the page, for now
+    }
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < kSlots / 32; ++i) {
+      const bool window = i < kWindow / 32;
+      const int blocks = window ? p.ori_blocks : p.cmp_blocks, page_rows = window ? kPage : p.cmp_page;
+      const bool live = column[i] >= 0;
+      const bool legal = column[i] < p.pages && (unsigned)resolved[i] < (unsigned)blocks;
+      bad |= live && !legal;
+      resolved[i] = live && legal ? resolved[i] * page_rows + within[i] : -1;
+    }
+    if (bad) report(p, kStatusBadPage, token, lane);
+    int live_chunks = 0;  // bit c set: chunk c holds a live slot (same in all lanes)
+#pragma unroll
+    for (int i = 0; i < kSlots / 32; ++i) {
+      rows[i * 32 + lane] = resolved[i];
+      if (__any_sync(0xffffffffu, resolved[i] >= 0)) live_chunks |= 1 << (i * 32 / kChunkRows);
     }
     if (lane == 0) {
       int count = 0;
@@ -273,7 +337,13 @@ __device__ void resolver_role(const Params& p, const Shared& sm) {
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(sm.bar(kTokenReady0 + buffer));
+    PROF_END(3);
+#ifdef SPARSE_MLA_PROFILE
+    if (token_count == 0) prof_[4] = clock64() - prof_start_;
+#endif
+    PROF_BEGIN;
   }
+  if (lane == 0) { PROF_FLUSH(p, 3); }
 }
 
 __device__ void producer_role(const Params& p, const Shared& sm) {
@@ -586,6 +656,7 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       PROF_BEGIN;
       if (threadIdx.x == 0) TRACE(sm, 21, i);
       tc_fence_after_sync();
+#ifndef SPARSE_MLA_EXPERIMENT_NO_SOFTMAX
       float s[64];
 #pragma unroll
       for (int c = 0; c < 64; c += 16)
@@ -640,6 +711,7 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
         for (int e = 0; e < 16; ++e) packed[e] = pack_pair<kFormat>(s[c * 32 + 2 * e], s[c * 32 + 2 * e + 1]);
         tmem_st16(s_addr + c * 16, packed);
       }
+#endif
       tmem_wait_st();
       tc_fence_before_sync();
       // Observe the previous chunk's PV completion before releasing this P: the PV barrier then
