@@ -103,10 +103,6 @@ __device__ __forceinline__ uint32_t swizzled(int row, int unit) {
   return (unit >> 3) * kBlockBytes + row * 128 + (((unit & 7) ^ (row & 7)) << 4);
 }
 
-__device__ __forceinline__ void producer_sync() {
-  asm volatile("bar.sync 1, %0;\n" ::"n"(kProducerThreads) : "memory");
-}
-
 struct Shared {
   uint32_t base;        // shared-space address of the 1024-aligned region
   unsigned char* ptr;   // generic pointer to the same
@@ -120,7 +116,6 @@ struct Shared {
   __device__ __forceinline__ volatile int* abort_flag() const {
     return reinterpret_cast<volatile int*>(ptr + kSmemMisc + 4);
   }
-  __device__ __forceinline__ int* scratch() const { return reinterpret_cast<int*>(ptr + kSmemMisc + 8); }
 };
 
 // The tokens of one persistent block, in order. Blocks take `group` consecutive tokens per round
@@ -215,7 +210,7 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 // ---- producer warps ---------------------------------------------------------------------------
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool live) {
-#ifdef SPARSE_MLA_EXPERIMENT_NO_COPY
+#ifdef SPARSE_MLA_EXPERIMENT_NO_COPY  // diagnostic build: measures the pipeline without gather traffic
   return;
 #endif
   // A masked slot is zero-filled (source size 0) so the tile never holds non-finite leftovers.
@@ -656,7 +651,7 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       PROF_BEGIN;
       if (threadIdx.x == 0) TRACE(sm, 21, i);
       tc_fence_after_sync();
-#ifndef SPARSE_MLA_EXPERIMENT_NO_SOFTMAX
+#ifndef SPARSE_MLA_EXPERIMENT_NO_SOFTMAX  // diagnostic build: barriers only, no softmax work
       float s[64];
 #pragma unroll
       for (int c = 0; c < 64; c += 16)
