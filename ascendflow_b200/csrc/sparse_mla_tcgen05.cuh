@@ -130,9 +130,9 @@ struct TokenWalk {
     while (true) {
       const int round = k / group;
       if ((long long)round * grid * group >= tokens) return -1;
-      const int token = (round * grid + block) * group + k % group;
+      const long long token = ((long long)round * grid + block) * group + k % group;
       ++k;
-      if (token < tokens) return token;
+      if (token < tokens) return int(token);
     }
   }
   __device__ __forceinline__ int peek() const { TokenWalk copy = *this; return copy.next(); }
