@@ -282,6 +282,7 @@ __device__ void resolver_role(const Params& p, const Shared& sm) {
     const int first_negative = __reduce_min_sync(0xffffffffu, first);
     PROF_END(2);
     PROF_BEGIN;
+    const int cmp_shift = p.cmp_page == 64 ? 6 : 7;
     // Same selection as resolve_window_slot / resolve_compressed_rank, in three passes so that
     // all block-table loads are in flight together (a branch or vote between them would
     // serialise twenty dependent round trips to memory): columns, loads, rows.
@@ -298,8 +299,9 @@ __device__ void resolver_role(const Params& p, const Shared& sm) {
     for (int i = 0; i < kTopK / 32; ++i) {
       const int rank = i * 32 + lane;
       const bool live = rank < g.bound && rank < first_negative && index[i] < g.cutoff;
-      column[kWindow / 32 + i] = live ? index[i] / p.cmp_page : -1;
-      within[kWindow / 32 + i] = index[i] % p.cmp_page;
+      // cmp_page is 64 or 128: shift and mask instead of a run-time division
+      column[kWindow / 32 + i] = live ? index[i] >> cmp_shift : -1;
+      within[kWindow / 32 + i] = index[i] & (p.cmp_page - 1);
     }
 #pragma unroll
     for (int i = 0; i < kSlots / 32; ++i) {
