@@ -28,6 +28,26 @@ __global__ void resolve_rows_kernel(const Params p, int32_t* resolved) {
   }
 }
 
+// Self-test of the bounded wait every role of the attention kernel uses: one warp waits on a
+// barrier that nobody arrives on; the wait must give up after `limit` clocks, record
+// kStatusWaitExpired and let the kernel return normally.
+__global__ void wait_expiry_kernel(int32_t* status, long long limit) {
+  __shared__ uint64_t barrier;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    sm100::mbar_init(sm100::smem_u32(&barrier), 1);
+    sm100::mbar_fence_init();
+    abort_flag = 0;
+  }
+  __syncthreads();
+  const bool arrived = sm100::mbar_wait(sm100::smem_u32(&barrier), 0, &abort_flag, limit);
+  __syncthreads();
+  if (threadIdx.x == 0 && !arrived && atomicCAS(status, kStatusOk, kStatusWaitExpired) == kStatusOk) {
+    status[1] = -1;
+    status[2] = abort_flag;
+  }
+}
+
 #define SPARSE_MLA_METADATA(NAME, DTYPE)                                                          \
   "{\"version\":1,\"name\":\"" NAME "\",\"target\":\"sm_100a\",\"kind\":\"mixed\",\"groups\":148," \
   "\"disjoint_external\":true,\"device_resources\":null,\"tensors\":["                            \
@@ -285,6 +305,15 @@ int launch_sparse_mla_static_workspace(void* stream, void* arg_q, void* arg_ori_
   // The array keeps whatever the previous call left: the status block must start at zero.
   if (int status = int(cudaMemsetAsync(workspace, 0, kStaticWorkspaceBytes, s))) return status;
   return umma::launch<1>(p, s, multiprocessors());
+}
+
+int launch_sparse_mla_wait_expiry_selftest(void* stream, void* npu_workspace, int64_t limit_cycles) {
+  if (npu_workspace == nullptr || limit_cycles <= 0 || limit_cycles > (int64_t(1) << 31)) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (int status = clear_workspace(s, npu_workspace)) return status;
+  wait_expiry_kernel<<<1, 32, 0, s>>>(reinterpret_cast<int32_t*>(static_cast<char*>(npu_workspace) + kWorkspaceStatusOffset),
+                                      (long long)limit_cycles);
+  return int(cudaGetLastError());
 }
 
 int read_status_sparse_mla(void* stream, void* npu_workspace, int32_t* host_words) {

@@ -172,6 +172,13 @@ int launch_sparse_mla_static_workspace(void* stream, void* arg_q, void* arg_ori_
                                        int64_t PAGES, int64_t ORI_BLOCKS, int64_t CMP_BLOCKS,
                                        int64_t CMP_PAGE);
 
+/* Self-test of the bounded on-chip wait (no counterpart in the reference, whose synchronisation
+ * is proven at compile time): one warp waits on a barrier nobody signals; after `limit_cycles`
+ * SM clocks (<= 2^31) it gives up, writes SPARSE_MLA_STATUS_WAIT_EXPIRED to the status block of
+ * `npu_workspace` and returns normally, leaving the context usable. The attention kernels use
+ * the same wait for every barrier, with a limit of 2^31 clocks (about a second). */
+int launch_sparse_mla_wait_expiry_selftest(void* stream, void* npu_workspace, int64_t limit_cycles);
+
 /* Copies the status block of a workspace to `host_words` (host, SPARSE_MLA_STATUS_WORDS int32)
  * after synchronising `stream`. word 0: a SPARSE_MLA_STATUS_* code, word 1: token, word 2: detail. */
 int read_status_sparse_mla(void* stream, void* npu_workspace, int32_t* host_words);

@@ -175,3 +175,35 @@ def test_upstream_shaped_entry(ops):
         sparse_flash_mla(*(tensors[n] for n in names), return_softmax_lse=True)
     with pytest.raises(CompileError, match="TND"):
         sparse_flash_mla(*(tensors[n] for n in names), layout_q="BSND")
+
+
+def test_bounded_wait_gives_up_and_reports_without_hanging(ops):
+    """Failure detection without a fault: a wait nobody satisfies expires, the status block says so,
+    and the same context keeps working."""
+    import ctypes as ct
+    import time
+
+    import torch
+
+    from ascendflow_b200.build import library_path
+    from ascendflow_b200.runtime.torch import _library
+
+    library = _library(library_path())
+    selftest = library.launch_sparse_mla_wait_expiry_selftest
+    selftest.argtypes, selftest.restype = [ct.c_void_p, ct.c_void_p, ct.c_int64], ct.c_int
+    read = library.read_status_sparse_mla
+    read.argtypes, read.restype = [ct.c_void_p, ct.c_void_p, ct.POINTER(ct.c_int32)], ct.c_int
+    workspace = torch.empty(1024, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    started = time.perf_counter()
+    assert selftest(stream, workspace.data_ptr(), 2_000_000) == 0   # about a millisecond of clocks
+    words = (ct.c_int32 * 8)()
+    assert read(stream, workspace.data_ptr(), words) == 0
+    assert time.perf_counter() - started < 5.0
+    assert words[0] == 2 and words[2] == 1
+    assert selftest(stream, workspace.data_ptr(), 0) == -1
+    # The context is intact: a normal call still runs and is correct.
+    policy = default_policy()
+    data = O.validation_inputs(policy, "mixed")
+    _, actual = run_case(ops, data, policy)
+    S.assert_close(actual, O.reference_fp32_from_data(data, policy), "after the expired wait")
