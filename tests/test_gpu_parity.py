@@ -207,3 +207,36 @@ def test_bounded_wait_gives_up_and_reports_without_hanging(ops):
     data = O.validation_inputs(policy, "mixed")
     _, actual = run_case(ops, data, policy)
     S.assert_close(actual, O.reference_fp32_from_data(data, policy), "after the expired wait")
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_randomised_requests(ops, seed):
+    """Random request mixes: ragged and empty requests, short caches, narrowed windows, padded,
+    duplicated, unsorted and causally incomplete indices, both compression ratios."""
+    rng = np.random.default_rng(1000 + seed)
+    ratio = int(rng.choice([1, 2]))
+    b = int(rng.integers(1, 7))
+    lens = [int(v) for v in rng.integers(0, 9, b)]
+    if sum(lens) == 0:
+        lens[0] = 3
+    max_seq = int(rng.choice([512, 1024, 4096]))
+    policy = O.make_policy(b, sum(lens), ratio=ratio, max_seq=max_seq, blocks=int(rng.integers(8, 48)))
+    data = O.validation_inputs(policy, str(rng.choice(["mixed", "padding", "duplicates", "replay", "sink"])), lens)
+    # Per-request cache lengths anywhere from "just the queries" to the table capacity.
+    lengths = np.array([int(rng.integers(max(n, 0), max_seq + 1)) for n in lens], dtype=np.int32)
+    if rng.random() < 0.3:
+        lengths[int(rng.integers(0, b))] = lens[int(rng.integers(0, b))]  # a cache holding only its queries
+    lengths = np.maximum(lengths, np.array(lens, dtype=np.int32))
+    data["seqused_ori_kv"] = lengths
+    data["seqused_cmp_kv"] = (lengths // ratio).astype(np.int32)
+    data["cmp_residual_kv"] = (lengths % ratio).astype(np.int32)
+    span = max(1, max_seq // ratio)
+    for token in range(policy["T"]):
+        count = int(rng.integers(0, 513))
+        row = np.full(512, -1, dtype=np.int32)
+        row[:count] = rng.integers(0, span, count)   # any order, duplicates, some beyond the cutoff
+        data["cmp_sparse_indices"][token, 0] = row
+        data["ori_topk_length"][token, 0] = int(rng.choice([0, 0, 1, 5, 64, 128]))
+    tensors, actual = run_case(ops, data, policy)
+    assert np.array_equal(resolved_on_device(ops, tensors, policy), O.resolve_rows(data, policy))
+    S.assert_close(actual, O.reference_fp32_from_data(data, policy), f"seed {seed}")
