@@ -57,6 +57,9 @@ def build_library(force=False, verbose=False):
     STAMP.write_text(identity)
     if verbose:
         print(result.stderr)
+    from . import gather_bench  # the isolated gather experiment is a second, small library
+
+    gather_bench.build()
     return LIBRARY
 
 

@@ -240,3 +240,12 @@ def test_randomised_requests(ops, seed):
     tensors, actual = run_case(ops, data, policy)
     assert np.array_equal(resolved_on_device(ops, tensors, policy), O.resolve_rows(data, policy))
     S.assert_close(actual, O.reference_fp32_from_data(data, policy), f"seed {seed}")
+
+
+def test_gather_experiment_rows_are_bit_exact():
+    """The isolated gather experiment (counterpart of the reference's gather study) checks its rows."""
+    from ascendflow_b200 import gather_bench
+
+    records = gather_bench.run(requests=8, queries=4, threads=(256,), depths=(2,), repeats=2)
+    assert len(records) == 2 and all(r["rows_exact"] for r in records)
+    assert {r["address"] for r in records} == {"lookup", "physical"}
