@@ -64,7 +64,10 @@ def build_library(force=False, verbose=False):
 
 
 def library_path():
-    """Path of the built library; fails loudly when it has not been built."""
+    """Path of the built library. A missing library is built if nvcc is here; otherwise this
+    fails loudly: there is no other implementation to fall back to."""
+    if not LIBRARY.exists() and nvcc() is not None:
+        build_library()
     require(LIBRARY.exists(),
             f"{LIBRARY} is missing: run `python -c 'import __graft_entry__ as g; g.build()'` "
             "(there is no CPU fallback)", kind=ErrorKind.RESOURCE)
