@@ -443,22 +443,22 @@ __device__ void producer_role(const Params& p, const Shared& sm) {
 
 // Compile-time unrolled issue loops: every operand offset and accumulate flag is an immediate,
 // so the issuing thread spends a couple of instructions per MMA and stays ahead of the pipe.
-template <int kFormat, int K>
+template <int kFormat, int K, int kEnd = kFeatures / 16>
 __device__ __forceinline__ void issue_qk_steps(uint32_t s_tmem, uint32_t q_tmem, uint64_t x_desc) {
-  if constexpr (K < kFeatures / 16) {
+  if constexpr (K < kEnd) {
     constexpr uint32_t half = (K >> 4) * kHalfLanes;
     constexpr uint32_t offset = (K >> 2) * kBlockBytes + (K & 3) * 32;
     mma_ts_c<(K & 15) != 0>(s_tmem + half, q_tmem + (K & 15) * 8 + half, x_desc + (offset >> 4), kIdescQK<kFormat>);
-    issue_qk_steps<kFormat, K + 1>(s_tmem, q_tmem, x_desc);
+    issue_qk_steps<kFormat, K + 1, kEnd>(s_tmem, q_tmem, x_desc);
   }
 }
 
 // S[buffer] = Q X^T for one 64-row tile, as two partial products: features 0-255 in lane half 0,
 // 256-511 in lane half 1. A = Q from tensor memory (8 columns of BF16 pairs per K=16 step).
-template <int kFormat>
+template <int kFormat, int kBegin = 0, int kEnd = kFeatures / 16>
 __device__ __forceinline__ void issue_qk(const Shared& sm, uint32_t tmem, int stage, int buffer) {
   const uint64_t x_desc = smem_desc_sw128(sm.base + kSmemKv + stage * kTileBytes, 16, 1024);
-  issue_qk_steps<kFormat, 0>(tmem + kTmemS + buffer * 64, tmem + kTmemQ, x_desc);
+  issue_qk_steps<kFormat, kBegin, kEnd>(tmem + kTmemS + buffer * 64, tmem + kTmemQ, x_desc);
 }
 
 template <int kFormat, int I, bool kFirst>
@@ -515,33 +515,50 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
       if (chunks == 1) mma_commit(sm.bar(kQFree));
       TRACE(sm, 14, 0);
     }
+    // The pipe's queue covers only ~150 cycles behind the short QK instructions, so nothing
+    // slow may sit between the last QK MMA of a chunk and the first PV MMA: barriers are tested
+    // (without blocking) a few MMAs before they are needed, and waited on only if that failed.
+    constexpr int kQkTail = 6;  // QK MMAs issued after the early test of the P barrier
+    bool kv_ready = false;      // the tile of the next QK has already been seen to have landed
     for (int i = 0; i < chunks; ++i, ++chunk_count, ++ring) {
+      const uint32_t stage = ring % kStages, c = chunk_count;
+      bool p_ready = false;
       if (i + 1 < chunks) {  // QK of the next chunk runs while the softmax warps work on this one
-        const uint32_t n = ring + 1, stage = n % kStages, use = n / kStages, c = chunk_count + 1;
+        const uint32_t n = ring + 1, next_stage = n % kStages, use = n / kStages, next = chunk_count + 1;
         PROF_BEGIN;
-        if (!mbar_wait(sm.bar(kKvFull0 + stage), use & 1, abort_flag)) return;
+        if (!kv_ready && !mbar_wait(sm.bar(kKvFull0 + next_stage), use & 1, abort_flag)) return;
         PROF_END(2);
         tc_fence_after_sync();
         TRACE(sm, 13, i + 1);
         PROF_BEGIN;
-        // The S buffer it overwrites held P of chunk c - 2, whose PV was issued before: in order.
-        issue_qk<kFormat>(sm, tmem, stage, c & 1);
+        // The S buffer it overwrites held P of chunk next - 2, whose PV was issued before: in order.
+        issue_qk<kFormat, 0, kFeatures / 16 - kQkTail>(sm, tmem, next_stage, next & 1);
+        if (i > 0) p_ready = mbar_test(sm.bar(kPFull0 + (c & 1)), (c >> 1) & 1);
+        if (p_ready) tc_fence_after_sync();
+        issue_qk<kFormat, kFeatures / 16 - kQkTail, kFeatures / 16>(sm, tmem, next_stage, next & 1);
         PROF_END(3);
-        mma_commit(sm.bar(kSFull0 + (c & 1)));
+        mma_commit(sm.bar(kSFull0 + (next & 1)));
         if (i + 2 == chunks) mma_commit(sm.bar(kQFree));
         TRACE(sm, 14, i + 1);
       }
-      const uint32_t stage = ring % kStages, c = chunk_count;
       if (i == 0) {  // the previous token's epilogue must have read O
         PROF_BEGIN;
         if (!mbar_wait(sm.bar(kOFree), (working_tokens & 1) ^ 1, abort_flag)) return;
         PROF_END(4);
       }
       TRACE(sm, 10, i);
-      PROF_BEGIN;
-      if (!mbar_wait(sm.bar(kPFull0 + (c & 1)), (c >> 1) & 1, abort_flag)) return;
-      PROF_END(5);
-      tc_fence_after_sync();
+      if (!p_ready) {
+        PROF_BEGIN;
+        if (!mbar_wait(sm.bar(kPFull0 + (c & 1)), (c >> 1) & 1, abort_flag)) return;
+        PROF_END(5);
+        tc_fence_after_sync();
+      }
+      // Look at the tile of the QK that follows this PV now, so that no wait separates them.
+      kv_ready = false;
+      if (i + 2 < chunks) {
+        const uint32_t n = ring + 2;
+        kv_ready = mbar_test(sm.bar(kKvFull0 + n % kStages), (n / kStages) & 1);
+      }
       TRACE(sm, 11, i);
       PROF_BEGIN;
       issue_pv<kFormat>(sm, tmem, stage, c & 1, i > 0);
