@@ -7,12 +7,12 @@
 // order, as the reference does: examples/sparse_attention/attention.py:42-64, 147-207):
 //
 //   resolver warp    resolves slot -> physical row (sparse_mla_common.cuh) up to two tokens ahead.
-//   producer warps   gather the token's Q tile and then its rows with 16-byte cp.async into a
-//                    three-stage ring of 128-byte-swizzled shared tiles. A row is fetched once
-//                    and serves as K and V.
+//   producer warps   gather the token's rows with 16-byte cp.async into a three-stage ring of
+//                    128-byte-swizzled shared tiles (a row is fetched once and serves as K and
+//                    V), and move the token's Q from global to tensor memory through registers.
 //   MMA warp         one thread issues S = Q X^T and O += P X. Q and P are read from tensor
 //                    memory, X from the shared tile (K-major for QK, MN-major for PV).
-//   softmax warps    move the token's Q into tensor memory, tcgen05.ld S, joint online softmax
+//   softmax warps    tcgen05.ld S, joint online softmax
 //                    with the per-head sink (examples/sparse_attention/attention.py:398-490: one
 //                    maximum and one denominator over window, compressed rows and sink; P rounded
 //                    to BF16 before PV, denominator from unrounded FP32), P back to tensor
@@ -36,6 +36,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <type_traits>
 #include <cuda_fp16.h>
 
 #include "sparse_mla_common.cuh"
@@ -90,7 +91,7 @@ struct TokenInfo {
 enum Bar {
   kTokenReady0 = 0, kTokenReady1, kTokenDone0, kTokenDone1, kQFull, kQFree,
   kKvFull0, kKvFull1, kKvFull2, kKvFree0, kKvFree1, kKvFree2,
-  kSFull0, kSFull1, kPFull0, kPFull1, kODone, kOFree, kQStageFree0, kQStageFree1, kQStageFree2, kBarCount
+  kSFull0, kSFull1, kPFull0, kPFull1, kODone, kOFree, kBarCount
 };
 
 // Storage formats of kind::f16 instructions: 0 = IEEE half, 1 = BF16.
@@ -173,35 +174,6 @@ __device__ __forceinline__ void trace(const Shared& sm, int event, int value) {
 #define PROF_FLUSH(p, role) do {} while (0)
 #endif
 
-// A producer wait whose outcome is the same for all producer threads: if any of them gave up,
-// all of them leave (a thread that returned alone would strand the others at the next bar.sync).
-__device__ __forceinline__ bool producer_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  const uint32_t ok = mbar_wait(bar, parity, abort_flag) ? 1u : 0u;
-  uint32_t failed;
-  asm volatile(
-      "{\n"
-      ".reg .pred p, q;\n"
-      "setp.eq.u32 q, %1, 0;\n"
-      "bar.red.or.pred p, 1, %2, q;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n" : "=r"(failed) : "r"(ok), "n"(kProducerThreads) : "memory");
-  return failed == 0;
-}
-
-// True when the phase has completed already, with the same answer for all producer threads.
-__device__ __forceinline__ bool producer_poll(uint32_t bar, uint32_t parity) {
-  const uint32_t ok = mbar_test(bar, parity) ? 1u : 0u;
-  uint32_t all;
-  asm volatile(
-      "{\n"
-      ".reg .pred p, q;\n"
-      "setp.ne.u32 q, %1, 0;\n"
-      "bar.red.and.pred p, 1, %2, q;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n" : "=r"(all) : "r"(ok), "n"(kProducerThreads) : "memory");
-  return all != 0;
-}
-
 // A wait whose outcome is uniform across the calling warp (all 32 lanes must call it).
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
@@ -215,6 +187,12 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool l
 #endif
   // A masked slot is zero-filled (source size 0) so the tile never holds non-finite leftovers.
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(live ? 16 : 0));
+}
+
+// Arrive on `bar` once all cp.async copies this thread has issued so far have completed. The
+// arrival counts towards the barrier's expected count (no pending-count increment).
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory");
 }
 
 // Warp-cooperative form of `token_geometry`: the request search probes 32 positions of
@@ -343,7 +321,29 @@ __device__ void resolver_role(const Params& p, const Shared& sm) {
   if (lane == 0) { PROF_FLUSH(p, 3); }
 }
 
-__device__ void producer_role(const Params& p, const Shared& sm) {
+// 8 x 8 transpose of 16-byte elements across the eight lanes of an octet: on entry lane a holds
+// element (a, b) ... of row b in words[4 b .. 4 b + 3]; on return it holds element (b, a) there,
+// i.e. what lane b held at index a. Three butterfly stages, register indices all static.
+__device__ __forceinline__ void transpose_octet(uint32_t* words, int lane) {
+#pragma unroll
+  for (int m = 1; m < 8; m <<= 1) {
+    const bool upper = (lane & m) != 0;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      if (b & m) continue;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        uint32_t& low = words[4 * b + w];
+        uint32_t& high = words[4 * (b | m) + w];
+        const uint32_t send = upper ? low : high;
+        const uint32_t got = __shfl_xor_sync(0xffffffffu, send, m);
+        if (upper) low = got; else high = got;
+      }
+    }
+  }
+}
+
+__device__ void producer_role(const Params& p, const Shared& sm, uint32_t tmem) {
   const int tid = threadIdx.x - kFirstProducerWarp * 32;
   const int lane = tid & 31;
   volatile int* abort_flag = sm.abort_flag();
@@ -351,87 +351,105 @@ __device__ void producer_role(const Params& p, const Shared& sm) {
   const long long prof_start_ = clock64(); (void)prof_start_;
   const char* window_base = static_cast<const char*>(p.ori_kv);
   const char* compressed_base = static_cast<const char*>(p.cmp_kv);
-  // Ring bookkeeping. A stage is released either by the MMA warp (a KV tile, kKvFree) or by the
-  // softmax warps (a Q tile, kQStageFree); each of those barriers advances only with its own
-  // kind of tile, so per stage we remember which barrier and which phase parity frees it next.
-  uint32_t ring = 0;  // tiles placed so far (all tokens): a Q tile per working token, then its chunks
-  uint32_t occupied = 0, last_is_q = 0, last_parity = 0, next_parity_kv = 0, next_parity_q = 0;
-  uint32_t token_count = 0;
-  int pending = -1;  // stage whose copies are in flight and not yet announced
+  // Q goes from global memory to tensor memory through registers, never through the ring. A warp
+  // reaches the 32 tensor-memory lanes of subpartition (warp index % 4): two producer warps
+  // share each subpartition and take 64 columns (256 bytes of every half row) each. Lane l of a
+  // subpartition holds head 16 * subpartition + (l & 15), feature half l >> 4.
+  const int warp = threadIdx.x >> 5;
+  const int subpartition = warp & 3, part = (warp - kFirstProducerWarp) >> 2;
+  // Loads are coalesced: in load j the eight lanes of an octet read 128 contiguous bytes of the
+  // half row that belongs to the octet's lane (j & 7); an 8 x 8 transpose by shuffles within
+  // the octet then gives every lane its own half row (see `transpose_octet`).
+  const size_t q_octet_offset = (size_t)(subpartition * 16 + (lane & 8)) * kRowBytes + (lane >> 4) * 512 + part * 256 + (lane & 7) * 16;
+  const uint32_t q_tmem = tmem + kTmemQ + part * 64 + (uint32_t(subpartition * 32) << 16);
+  // Ring bookkeeping: stage s is free again once the PV of the tile it held has completed
+  // (kKvFree0 + s, committed by the MMA thread). A tile is announced without anybody waiting
+  // for it: every producer thread attaches the completion of its own copies to the stage's
+  // full barrier (cp.async.mbarrier.arrive), so the threads never block on data in flight and
+  // the warps need not stay in step with each other.
+  uint32_t ring = 0;  // tiles placed so far (all tokens)
+  uint32_t token_count = 0, q_loads = 0;
+  // Q staging registers: `words` holds (part of) the Q slice of `staged_token`; step s < 4 loads
+  // a quarter of it, steps 4 and 5 transpose the two halves.
+  constexpr int kQSteps = 6;
+  constexpr int kQFirstItem = 2;  // the first two tiles of a token are issued without delay
+  uint32_t words[64];
+  int staged_token = -1, q_step = kQSteps;
+  auto q_advance = [&]() {
+    const char* source = static_cast<const char*>(p.q) + (size_t)staged_token * kHeads * kRowBytes + q_octet_offset;
+    auto load4 = [&](auto first) {
+      constexpr int kFirst = decltype(first)::value;
+#pragma unroll
+      for (int j = kFirst; j < kFirst + 4; ++j) {  // row (j & 7) of the octet, units 8 (j >> 3) .. + 7
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(source + (size_t)(j & 7) * kRowBytes + (j >> 3) * 128));
+        words[4 * j + 0] = v.x; words[4 * j + 1] = v.y; words[4 * j + 2] = v.z; words[4 * j + 3] = v.w;
+      }
+    };
+    switch (q_step) {
+      case 0: load4(std::integral_constant<int, 0>{}); break;
+      case 1: load4(std::integral_constant<int, 4>{}); break;
+      case 2: load4(std::integral_constant<int, 8>{}); break;
+      case 3: load4(std::integral_constant<int, 12>{}); break;
+      case 4: transpose_octet(words, lane); break;
+      default: transpose_octet(words + 32, lane); break;
+    }
+    ++q_step;
+  };
   TokenWalk walk(p);
   for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
-    if (pending >= 0 && !producer_poll(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1)) {
-      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + pending));
-      pending = -1;
-    }
     PROF_BEGIN;
-    if (!producer_wait(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
+    if (!warp_wait(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
     PROF_END(0);
     const int* rows = sm.rows(token_count & 1);
     const TokenInfo* info = sm.info(token_count & 1);
     const int chunks = info->chunks;
-    const char* q = static_cast<const char*>(p.q) + (size_t)token * kHeads * kRowBytes;
-    for (int item = chunks > 0 ? -1 : 0; item < chunks; ++item, ++ring) {
-      const uint32_t stage = ring % kStages, bit = 1u << stage;
-      const bool is_q = item < 0;
-      if (occupied & bit) {
-        const uint32_t bar = sm.bar(((last_is_q & bit) ? kQStageFree0 : kKvFree0) + stage);
-        const uint32_t parity = (last_parity >> stage) & 1u;
-        if (pending >= 0 && !producer_poll(bar, parity)) {
-          // The ring is full: announce the copies in flight before blocking on a free stage.
-          asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-          fence_proxy_async();
-          __syncwarp();
-          if (tid == 0) TRACE(sm, 5, item - 1);
-          if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + pending));
-          pending = -1;
-        }
-        PROF_BEGIN;
-        if (!producer_wait(bar, parity, abort_flag)) return;
-        PROF_END(1);
-      }
+    for (int item = 0; item < chunks; ++item, ++ring) {
+      const uint32_t stage = ring % kStages, use = ring / kStages;
       PROF_BEGIN;
-      occupied |= bit;
-      const uint32_t next_parity = is_q ? next_parity_q : next_parity_kv;
-      last_parity = (last_parity & ~bit) | (next_parity & bit);
-      if (is_q) { next_parity_q ^= bit; last_is_q |= bit; } else { next_parity_kv ^= bit; last_is_q &= ~bit; }
+      if (use > 0 && !warp_wait(sm.bar(kKvFree0 + stage), (use - 1) & 1, abort_flag)) return;
+      PROF_END(1);
+      PROF_BEGIN;
       if (tid == 0) TRACE(sm, 4, item);
       const uint32_t tile = sm.base + kSmemKv + stage * kTileBytes;
       const int unit = tid & 63;
-      if (is_q) {
-        for (int r = tid >> 6; r < kHeads; r += kProducerThreads / 64)
-          cp_async16(tile + swizzled(r, unit), q + (size_t)r * kRowBytes + unit * 16, true);
-      } else {
-        const int chunk = info->chunk[item];
-        for (int r = tid >> 6; r < kChunkRows; r += kProducerThreads / 64) {
-          const int slot = chunk * kChunkRows + r;
-          const int row = rows[slot];
-          const char* base = slot < kWindow ? window_base : compressed_base;
-          cp_async16(tile + swizzled(r, unit), base + (size_t)(row < 0 ? 0 : row) * kRowBytes + unit * 16, row >= 0);
-        }
+      const int chunk = info->chunk[item];
+      for (int r = tid >> 6; r < kChunkRows; r += kProducerThreads / 64) {
+        const int slot = chunk * kChunkRows + r;
+        const int row = rows[slot];
+        const char* base = slot < kWindow ? window_base : compressed_base;
+        cp_async16(tile + swizzled(r, unit), base + (size_t)(row < 0 ? 0 : row) * kRowBytes + unit * 16, row >= 0);
       }
-      asm volatile("cp.async.commit_group;\n" ::: "memory");
+      cp_async_arrive(sm.bar(kKvFull0 + stage));
       PROF_END(2);
-      PROF_BEGIN;
-      if (pending >= 0) {  // the previous tile has landed once at most one group is outstanding
-        asm volatile("cp.async.wait_group 1;\n" ::: "memory");
-        fence_proxy_async();
+      if (item == 0) {
+        // The token's Q, right behind its first tile. Its registers were filled while the
+        // previous token's tiles were being issued, unless this is the block's first working
+        // token or the walk skipped an empty one. The wait (the previous working token's last
+        // QK has read the old Q) cannot depend on this thread: all its tiles have been issued.
+        PROF_BEGIN;
+        if (staged_token != token) { staged_token = token; q_step = 0; }
+        while (q_step < kQSteps) q_advance();
+        PROF_END(4);
+        PROF_BEGIN;
+        if (q_loads > 0 && !warp_wait(sm.bar(kQFree), (q_loads - 1) & 1, abort_flag)) return;
+        PROF_END(5);
+        PROF_BEGIN;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          tmem_st16(q_tmem + j * 16, *reinterpret_cast<uint32_t(*)[16]>(&words[16 * j]));
+        tmem_wait_st();
+        tc_fence_before_sync();
         __syncwarp();
-        if (tid == 0) TRACE(sm, 5, item - 1);
-        if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + pending));
+        if (lane == 0) mbar_arrive(sm.bar(kQFull));
+        ++q_loads;
+        staged_token = walk.peek();  // start on the next token's Q
+        q_step = staged_token >= 0 ? 0 : kQSteps;
+        PROF_END(6);
+      } else if (item >= kQFirstItem && q_step < kQSteps) {
+        q_advance();  // one slice of the next token's Q per tile, so that it never comes as a burst
       }
-      PROF_END(3);
-      pending = int(stage);
     }
-  }
-  if (pending >= 0) {
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-    fence_proxy_async();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + pending));
   }
 #ifdef SPARSE_MLA_PROFILE
   prof_[7] = clock64() - prof_start_;
@@ -487,8 +505,8 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
   volatile int* abort_flag = sm.abort_flag();
   PROF_DECL;
   const long long prof_start_ = clock64(); (void)prof_start_;
-  // `ring` counts tiles in the shared ring (a Q tile per working token, then its chunks);
-  // `chunk_count` counts KV chunks only and selects the S / P buffer.
+  // `ring` counts tiles in the shared ring, `chunk_count` selects the S / P buffer (the same
+  // sequence; kept apart because the two wrap differently).
   uint32_t ring = 0, chunk_count = 0, token_count = 0, working_tokens = 0;
   TokenWalk walk(p);
   for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
@@ -497,7 +515,6 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
     PROF_END(0);
     const int chunks = sm.info(token_count & 1)->chunks;
     if (chunks == 0) continue;
-    ++ring;  // the token's Q tile: consumed by the softmax warps
     PROF_BEGIN;
     if (!mbar_wait(sm.bar(kQFull), working_tokens & 1, abort_flag)) return;
     PROF_END(1);
@@ -588,24 +605,6 @@ __device__ __forceinline__ uint32_t pack_pair(float a, float b) {  // two FP32 -
   }
 }
 
-// Copy this thread's half row of Q (256 BF16 = 128 words) from a staged shared tile (same
-// swizzled layout as a KV tile: row = head) to tensor memory.
-__device__ __forceinline__ void load_q_half_row(const Shared& sm, uint32_t tmem_q, int stage, int head, int half) {
-  const unsigned char* tile = sm.ptr + kSmemKv + stage * kTileBytes;
-#pragma unroll
-  for (int block = 0; block < 4; ++block) {
-    uint32_t words[32];
-#pragma unroll
-    for (int unit = 0; unit < 8; ++unit) {
-      const uint4 v = *reinterpret_cast<const uint4*>(tile + swizzled(head, (half * 4 + block) * 8 + unit));
-      words[unit * 4 + 0] = v.x; words[unit * 4 + 1] = v.y; words[unit * 4 + 2] = v.z; words[unit * 4 + 3] = v.w;
-    }
-    tmem_st16(tmem_q + block * 32, *reinterpret_cast<uint32_t(*)[16]>(&words[0]));
-    tmem_st16(tmem_q + block * 32 + 16, *reinterpret_cast<uint32_t(*)[16]>(&words[16]));
-  }
-  tmem_wait_st();
-}
-
 template <int kFormat>
 __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -616,47 +615,24 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   PROF_DECL;
   const long long prof_start_ = clock64(); (void)prof_start_;
   const float sink = __ldg(p.sinks + head) * 1.4426950408889634f;  // log2 domain
-  uint32_t ring = 0, chunk_count = 0, token_count = 0, pv_waited = 0, q_loads = 0;
+  uint32_t chunk_count = 0, token_count = 0, pv_waited = 0;
   __nv_bfloat16* out_base = static_cast<__nv_bfloat16*>(p.out);
 
-  // Wait for a token's row list; if it has work, move its Q into tensor memory once the QKs of
-  // the previous working token have finished reading the old one. Returns false on a failed wait.
-  auto prepare = [&](int token, uint32_t count) -> bool {
-    if (!warp_wait(sm.bar(kTokenReady0 + (count & 1)), (count >> 1) & 1, abort_flag)) return false;
-    if (sm.info(count & 1)->chunks == 0) return true;
-    const uint32_t stage = ring % kStages, use = ring / kStages;
-    if (!warp_wait(sm.bar(kKvFull0 + stage), use & 1, abort_flag)) return false;
-    if (q_loads > 0 && !warp_wait(sm.bar(kQFree), (q_loads - 1) & 1, abort_flag)) return false;
-    tc_fence_after_sync();
-    load_q_half_row(sm, tmem + kTmemQ + lane_base, stage, head, half);
-    tc_fence_before_sync();
-    __syncwarp();
-    if (lane == 0) {
-      mbar_arrive(sm.bar(kQStageFree0 + stage));
-      mbar_arrive(sm.bar(kQFull));
-    }
-    ++q_loads;
-    ++ring;
-    return true;
-  };
-
   TokenWalk walk(p);
-  if (walk.peek() >= 0 && !prepare(walk.peek(), 0)) return;
   for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
+    if (!warp_wait(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
     const TokenInfo* info = sm.info(token_count & 1);
     const int* rows = sm.rows(token_count & 1);
     const int chunks = info->chunks;
-    const int next = walk.peek();
     __nv_bfloat16* out = out_base + ((size_t)token * kHeads + head) * kFeatures + half * 256;
     if (chunks == 0) {  // nothing visible: the output row is zero whatever the sink
       for (int i = 0; i < 256; i += 8) *reinterpret_cast<uint4*>(out + i) = make_uint4(0, 0, 0, 0);
-      if (next >= 0 && !prepare(next, token_count + 1)) return;
       __syncwarp();
       if (lane == 0) mbar_arrive(sm.bar(kTokenDone0 + (token_count & 1)));
       continue;
     }
     float run_max = sink, run_sum = 1.f;  // the sink's own weight exp2(sink - run_max)
-    for (int i = 0; i < chunks; ++i, ++chunk_count, ++ring) {
+    for (int i = 0; i < chunks; ++i, ++chunk_count) {
       const uint32_t buffer = chunk_count & 1;
       const int chunk = info->chunk[i];
       const unsigned live_lo = __ballot_sync(0xffffffffu, rows[chunk * kChunkRows + lane] >= 0);
@@ -728,6 +704,8 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
 #endif
       tmem_wait_st();
       tc_fence_before_sync();
+      PROF_END(1);
+      PROF_BEGIN;
       // Observe the previous chunk's PV completion before releasing this P: the PV barrier then
       // never runs more than one phase ahead of this warp.
       while (pv_waited < chunk_count) {
@@ -735,15 +713,11 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
         ++pv_waited;
       }
       __syncwarp();
-      PROF_END(1);
+      PROF_END(2);
       if (threadIdx.x == 0) TRACE(sm, 22, i);
       if (lane == 0) mbar_arrive(sm.bar(kPFull0 + buffer));
     }
 
-    // Next token's Q goes to tensor memory while the last PV of this one runs.
-    PROF_BEGIN;
-    if (next >= 0 && !prepare(next, token_count + 1)) return;
-    PROF_END(2);
     PROF_BEGIN;
 
     // ---- epilogue: O / denominator -> BF16 -> global ------------------------------------------
@@ -815,8 +789,8 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm.ptr + kSmemMisc);
 
   if (threadIdx.x == 0) {
-    const int P = kProducerWarps, S = kSoftmaxWarps;
-    const int counts[kBarCount] = {1, 1, S, S, S, 1, P, P, P, 1, 1, 1, 1, 1, S, S, 1, S, S, S, S};
+    const int P = kProducerWarps, S = kSoftmaxWarps, T = kProducerThreads;
+    const int counts[kBarCount] = {1, 1, S, S, P, 1, T, T, T, 1, 1, 1, 1, 1, S, S, 1, S};
     for (int i = 0; i < kBarCount; ++i) mbar_init(sm.bar(i), counts[i]);
     mbar_fence_init();
     *sm.abort_flag() = 0;
@@ -838,7 +812,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
   } else if (warp == kResolverWarp) {
     resolver_role(p, sm);
   } else {
-    producer_role(p, sm);
+    producer_role(p, sm, tmem);
     asm volatile("cp.async.wait_all;\n" ::: "memory");
   }
 
