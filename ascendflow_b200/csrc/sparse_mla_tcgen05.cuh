@@ -63,23 +63,27 @@ constexpr int kTileBytes = 8 * kBlockBytes;                 // 64 rows x 512 fea
 
 // Shared memory map (bytes from a 1024-aligned base).
 constexpr int kSmemKv = 0;
-constexpr int kSmemRows = kSmemKv + kStages * kTileBytes;   // int[2][640]
+// Per softmax warp 4 KiB: the epilogue's 32 x 128-byte staging rows. The same bytes hold the two
+// P tiles between epilogues (see `p_offset`): a warp only ever touches its own 4 KiB of either.
+// 1024-byte aligned like the tiles, because the swizzle is a function of the address.
+constexpr int kSmemStore = kSmemKv + kStages * kTileBytes;
+constexpr int kSmemRows = kSmemStore + kSoftmaxWarps * 4096;   // int[2][640]
 constexpr int kSmemInfo = kSmemRows + 2 * kSlots * 4;       // TokenInfo[2]
 constexpr int kSmemBars = kSmemInfo + 2 * 64;               // mbarriers
 constexpr int kSmemMisc = kSmemBars + 32 * 8;               // tmem slot, abort flag
-constexpr int kSmemStore = kSmemMisc + 64;                  // per softmax warp: 32 x 128-byte staging rows
+constexpr int kSmemEnd = kSmemMisc + 64;
 #ifdef SPARSE_MLA_TRACE
 constexpr int kTraceEntries = 900;
-constexpr int kSmemTrace = kSmemStore + kSoftmaxWarps * 4096;
+constexpr int kSmemTrace = kSmemEnd;
 constexpr int kSmemBytes = kSmemTrace + 16 + kTraceEntries * 8 + 1024;
 #else
-constexpr int kSmemBytes = kSmemStore + kSoftmaxWarps * 4096 + 1024;  // + slack for the 1024-byte alignment
+constexpr int kSmemBytes = kSmemEnd + 1024;  // + slack for the 1024-byte alignment
 #endif
 
 constexpr uint32_t kTmemColumns = 512;
 constexpr uint32_t kTmemO = 0;
 constexpr uint32_t kTmemQ = 256;
-constexpr uint32_t kTmemS = 384;                             // buffer b at column 384 + 64 b
+constexpr uint32_t kTmemS = 384;                             // one 128-column score buffer
 constexpr uint32_t kHalfLanes = 16u << 16;                   // lane offset of half 1 in a tensor-memory address
 
 struct TokenInfo {
@@ -91,17 +95,31 @@ struct TokenInfo {
 enum Bar {
   kTokenReady0 = 0, kTokenReady1, kTokenDone0, kTokenDone1, kQFull, kQFree,
   kKvFull0, kKvFull1, kKvFull2, kKvFree0, kKvFree1, kKvFree2,
-  kSFull0, kSFull1, kPFull0, kPFull1, kODone, kOFree, kBarCount
+  kSFull, kSFree, kPFull0, kPFull1, kODone, kOFree, kBarCount
 };
 
 // Storage formats of kind::f16 instructions: 0 = IEEE half, 1 = BF16.
-template <int kFormat> constexpr uint32_t kIdescQK = idesc_f16(64, 64, kFormat, 0, 0);
+template <int kFormat> constexpr uint32_t kIdescQK = idesc_f16(128, 128, kFormat, 0, 0);
 template <int kFormat> constexpr uint32_t kIdescPV = idesc_f16(64, 256, kFormat, 0, 1);
+
+// Position of 64-feature block b in a tile: blocks b and b + 4 (the same features of the low
+// and the high half of a row) are neighbours, so that a K-major operand of 128 "rows" with
+// 8-row groups 1024 bytes apart reads rows 0-63 from block b and rows 64-127 from block b + 4.
+__host__ __device__ constexpr int block_position(int b) { return (b & 3) * 2 + (b >> 2); }
 
 // Byte offset of 16-byte unit `unit` (0..63) of row `row` in a K-major 128-byte-swizzled tile
 // of 64 rows: eight 64-feature blocks of [64 rows x 128 bytes].
 __device__ __forceinline__ uint32_t swizzled(int row, int unit) {
-  return (unit >> 3) * kBlockBytes + row * 128 + (((unit & 7) ^ (row & 7)) << 4);
+  return block_position(unit >> 3) * kBlockBytes + row * 128 + (((unit & 7) ^ (row & 7)) << 4);
+}
+
+// P tile `buffer` (64 heads x 64 rows of 16-bit probabilities, K-major, 128-byte swizzle: one
+// 128-byte row per head): byte offset of 16-byte unit `unit` (0..7) of head `head` from
+// kSmemStore. Eight-head groups are 2048 bytes apart and the two buffers interleave at 1024, so
+// the heads 16 w .. 16 w + 15 of softmax warp w lie inside that warp's own 4 KiB.
+constexpr int kPGroupBytes = 2048;
+__device__ __forceinline__ uint32_t p_offset(int buffer, int head, int unit) {
+  return (head >> 3) * kPGroupBytes + buffer * 1024 + (head & 7) * 128 + ((unit ^ (head & 7)) << 4);
 }
 
 struct Shared {
@@ -461,43 +479,51 @@ __device__ void producer_role(const Params& p, const Shared& sm, uint32_t tmem) 
 
 // Compile-time unrolled issue loops: every operand offset and accumulate flag is an immediate,
 // so the issuing thread spends a couple of instructions per MMA and stays ahead of the pipe.
-template <int kFormat, int K, int kEnd = kFeatures / 16>
+constexpr int kQkSteps = kFeatures / 32;  // K = 16 steps over one half of the features
+template <int kFormat, int K, int kEnd = kQkSteps>
 __device__ __forceinline__ void issue_qk_steps(uint32_t s_tmem, uint32_t q_tmem, uint64_t x_desc) {
   if constexpr (K < kEnd) {
-    constexpr uint32_t half = (K >> 4) * kHalfLanes;
-    constexpr uint32_t offset = (K >> 2) * kBlockBytes + (K & 3) * 32;
-    mma_ts_c<(K & 15) != 0>(s_tmem + half, q_tmem + (K & 15) * 8 + half, x_desc + (offset >> 4), kIdescQK<kFormat>);
+    constexpr uint32_t offset = block_position(K >> 2) * kBlockBytes + (K & 3) * 32;
+    mma_ts_c<K != 0>(s_tmem, q_tmem + K * 8, x_desc + (offset >> 4), kIdescQK<kFormat>);
     issue_qk_steps<kFormat, K + 1, kEnd>(s_tmem, q_tmem, x_desc);
   }
 }
 
-// S[buffer] = Q X^T for one 64-row tile, as two partial products: features 0-255 in lane half 0,
-// 256-511 in lane half 1. A = Q from tensor memory (8 columns of BF16 pairs per K=16 step).
-template <int kFormat, int kBegin = 0, int kEnd = kFeatures / 16>
-__device__ __forceinline__ void issue_qk(const Shared& sm, uint32_t tmem, int stage, int buffer) {
+// S = Q X^T for one 64-row tile as ONE M = 128, N = 128 product per K step. Operand rows
+// (tensor-memory lanes) 16-31 of every subpartition hold the high feature half of the heads
+// whose low half is in lanes 0-15; operand "rows" 64-127 of B are the tile's rows again, high
+// feature half (block b + 4 next to block b). Of the 128 x 128 result a thread's useful scores
+// are columns 0-63 in a low-half lane (Q_lo . X_lo) and 64-127 in a high-half lane
+// (Q_hi . X_hi); the other two quadrants mix the halves and are ignored. Half the products are
+// thrown away, but M = 128 runs at the full rate of the pipe and N = 128 is above its
+// per-instruction floor: 16 instructions of 64 cycles replace 32 of about 56.
+template <int kFormat, int kBegin = 0, int kEnd = kQkSteps>
+__device__ __forceinline__ void issue_qk(const Shared& sm, uint32_t tmem, int stage) {
   const uint64_t x_desc = smem_desc_sw128(sm.base + kSmemKv + stage * kTileBytes, 16, 1024);
-  issue_qk_steps<kFormat, kBegin, kEnd>(tmem + kTmemS + buffer * 64, tmem + kTmemQ, x_desc);
+  issue_qk_steps<kFormat, kBegin, kEnd>(tmem + kTmemS, tmem + kTmemQ, x_desc);
 }
 
 template <int kFormat, int I, bool kFirst>
-__device__ __forceinline__ void issue_pv_steps(uint32_t o_tmem, uint32_t p_tmem, uint64_t x_desc) {
+__device__ __forceinline__ void issue_pv_steps(uint32_t o_tmem, uint64_t p_desc, uint64_t x_desc) {
   if constexpr (I < 2 * (kChunkRows / 16)) {
     constexpr int h = I / (kChunkRows / 16), k = I % (kChunkRows / 16);
     constexpr uint32_t half = h * kHalfLanes;
-    constexpr uint32_t offset = h * 4 * kBlockBytes + k * 2048;
-    mma_ts_c<!(kFirst && k == 0)>(o_tmem + half, p_tmem + k * 8 + half, x_desc + (offset >> 4), kIdescPV<kFormat>);
-    issue_pv_steps<kFormat, I + 1, kFirst>(o_tmem, p_tmem, x_desc);
+    constexpr uint32_t offset = h * kBlockBytes + k * 2048;
+    mma_ss_c<!(kFirst && k == 0)>(o_tmem + half, p_desc + ((k * 32) >> 4), x_desc + (offset >> 4), kIdescPV<kFormat>);
+    issue_pv_steps<kFormat, I + 1, kFirst>(o_tmem, p_desc, x_desc);
   }
 }
 
-// O += P X for one 64-row tile: features 0-255 in lane half 0, 256-511 in lane half 1.
-// A = P from tensor memory (written to both halves by the softmax threads); B = X with features
-// contiguous: four 64-feature blocks kBlockBytes apart, 8-row groups 1024 bytes apart.
+// O += P X for one 64-row tile: features 0-255 accumulate in lane half 0, 256-511 in lane half 1.
+// A = P from shared memory (one 128-byte row per head, 32 bytes per K = 16 step); B = X with
+// features contiguous: the four 64-feature blocks of a half are two block positions apart,
+// 8-row groups 1024 bytes apart.
 template <int kFormat>
 __device__ __forceinline__ void issue_pv(const Shared& sm, uint32_t tmem, int stage, int buffer, bool accumulate) {
-  const uint64_t x_desc = smem_desc_sw128(sm.base + kSmemKv + stage * kTileBytes, kBlockBytes, 1024);
-  if (accumulate) issue_pv_steps<kFormat, 0, false>(tmem + kTmemO, tmem + kTmemS + buffer * 64, x_desc);
-  else issue_pv_steps<kFormat, 0, true>(tmem + kTmemO, tmem + kTmemS + buffer * 64, x_desc);
+  const uint64_t x_desc = smem_desc_sw128(sm.base + kSmemKv + stage * kTileBytes, 2 * kBlockBytes, 1024);
+  const uint64_t p_desc = smem_desc_sw128(sm.base + kSmemStore + buffer * 1024, 16, kPGroupBytes);
+  if (accumulate) issue_pv_steps<kFormat, 0, false>(tmem + kTmemO, p_desc, x_desc);
+  else issue_pv_steps<kFormat, 0, true>(tmem + kTmemO, p_desc, x_desc);
 }
 
 template <int kFormat>
@@ -505,9 +531,9 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
   volatile int* abort_flag = sm.abort_flag();
   PROF_DECL;
   const long long prof_start_ = clock64(); (void)prof_start_;
-  // `ring` counts tiles in the shared ring, `chunk_count` selects the S / P buffer (the same
-  // sequence; kept apart because the two wrap differently).
-  uint32_t ring = 0, chunk_count = 0, token_count = 0, working_tokens = 0;
+  // `chunk_count` counts chunks over all tokens: chunk c uses ring stage c % kStages, P tile
+  // c & 1, and the c-th phase of the score barriers.
+  uint32_t chunk_count = 0, token_count = 0, working_tokens = 0;
   TokenWalk walk(p);
   for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
     PROF_BEGIN;
@@ -519,42 +545,47 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
     if (!mbar_wait(sm.bar(kQFull), working_tokens & 1, abort_flag)) return;
     PROF_END(1);
     {  // first QK of the token
-      const uint32_t stage = ring % kStages, use = ring / kStages;
+      const uint32_t stage = chunk_count % kStages, use = chunk_count / kStages;
       PROF_BEGIN;
       if (!mbar_wait(sm.bar(kKvFull0 + stage), use & 1, abort_flag)) return;
+      // the softmax warps have taken the previous chunk's scores out of the single buffer
+      if (chunk_count > 0 && !mbar_wait(sm.bar(kSFree), (chunk_count - 1) & 1, abort_flag)) return;
       PROF_END(2);
       tc_fence_after_sync();
       TRACE(sm, 13, 0);
       PROF_BEGIN;
-      issue_qk<kFormat>(sm, tmem, stage, chunk_count & 1);
+      issue_qk<kFormat>(sm, tmem, stage);
       PROF_END(3);
-      mma_commit(sm.bar(kSFull0 + (chunk_count & 1)));
+      mma_commit(sm.bar(kSFull));
       if (chunks == 1) mma_commit(sm.bar(kQFree));
       TRACE(sm, 14, 0);
     }
-    // The pipe's queue covers only ~150 cycles behind the short QK instructions, so nothing
-    // slow may sit between the last QK MMA of a chunk and the first PV MMA: barriers are tested
-    // (without blocking) a few MMAs before they are needed, and waited on only if that failed.
-    constexpr int kQkTail = 6;  // QK MMAs issued after the early test of the P barrier
+    // The pipe's queue covers only ~150 cycles, so nothing slow may sit between the last QK MMA
+    // of a chunk and the first PV MMA: barriers are tested (without blocking) a few MMAs before
+    // they are needed, and waited on only if that failed.
+    constexpr int kQkTail = 4;  // QK MMAs issued after the early test of the P barrier
     bool kv_ready = false;      // the tile of the next QK has already been seen to have landed
-    for (int i = 0; i < chunks; ++i, ++chunk_count, ++ring) {
-      const uint32_t stage = ring % kStages, c = chunk_count;
+    for (int i = 0; i < chunks; ++i, ++chunk_count) {
+      const uint32_t c = chunk_count, stage = c % kStages;
       bool p_ready = false;
       if (i + 1 < chunks) {  // QK of the next chunk runs while the softmax warps work on this one
-        const uint32_t n = ring + 1, next_stage = n % kStages, use = n / kStages, next = chunk_count + 1;
+        const uint32_t next = c + 1, next_stage = next % kStages, use = next / kStages;
         PROF_BEGIN;
         if (!kv_ready && !mbar_wait(sm.bar(kKvFull0 + next_stage), use & 1, abort_flag)) return;
         PROF_END(2);
+        PROF_BEGIN;
+        // The score buffer is free once the softmax warps have read chunk c out of it.
+        if (!mbar_wait(sm.bar(kSFree), c & 1, abort_flag)) return;
+        PROF_END(4);
         tc_fence_after_sync();
         TRACE(sm, 13, i + 1);
         PROF_BEGIN;
-        // The S buffer it overwrites held P of chunk next - 2, whose PV was issued before: in order.
-        issue_qk<kFormat, 0, kFeatures / 16 - kQkTail>(sm, tmem, next_stage, next & 1);
+        issue_qk<kFormat, 0, kQkSteps - kQkTail>(sm, tmem, next_stage);
         if (i > 0) p_ready = mbar_test(sm.bar(kPFull0 + (c & 1)), (c >> 1) & 1);
         if (p_ready) tc_fence_after_sync();
-        issue_qk<kFormat, kFeatures / 16 - kQkTail, kFeatures / 16>(sm, tmem, next_stage, next & 1);
+        issue_qk<kFormat, kQkSteps - kQkTail, kQkSteps>(sm, tmem, next_stage);
         PROF_END(3);
-        mma_commit(sm.bar(kSFull0 + (next & 1)));
+        mma_commit(sm.bar(kSFull));
         if (i + 2 == chunks) mma_commit(sm.bar(kQFree));
         TRACE(sm, 14, i + 1);
       }
@@ -573,7 +604,7 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
       // Look at the tile of the QK that follows this PV now, so that no wait separates them.
       kv_ready = false;
       if (i + 2 < chunks) {
-        const uint32_t n = ring + 2;
+        const uint32_t n = c + 2;
         kv_ready = mbar_test(sm.bar(kKvFull0 + n % kStages), (n / kStages) & 1);
       }
       TRACE(sm, 11, i);
@@ -631,38 +662,57 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       if (lane == 0) mbar_arrive(sm.bar(kTokenDone0 + (token_count & 1)));
       continue;
     }
-    float run_max = sink, run_sum = 1.f;  // the sink's own weight exp2(sink - run_max)
+    // `run_sum` is this lane's share of the denominator; the low lane's share includes the
+    // sink's own weight exp2(sink - run_max) = 1.
+    float run_max = sink, run_sum = half ? 0.f : 1.f;
     for (int i = 0; i < chunks; ++i, ++chunk_count) {
       const uint32_t buffer = chunk_count & 1;
       const int chunk = info->chunk[i];
       const unsigned live_lo = __ballot_sync(0xffffffffu, rows[chunk * kChunkRows + lane] >= 0);
       const unsigned live_hi = __ballot_sync(0xffffffffu, rows[chunk * kChunkRows + 32 + lane] >= 0);
-      const uint32_t s_addr = tmem + kTmemS + buffer * 64 + lane_base;
+      const uint32_t s_addr = tmem + kTmemS + lane_base;
 
       if (threadIdx.x == 0) TRACE(sm, 20, i);
       PROF_BEGIN;
-      if (!warp_wait(sm.bar(kSFull0 + buffer), (chunk_count >> 1) & 1, abort_flag)) return;
+      if (!warp_wait(sm.bar(kSFull), chunk_count & 1, abort_flag)) return;
       PROF_END(0);
       PROF_BEGIN;
       if (threadIdx.x == 0) TRACE(sm, 21, i);
       tc_fence_after_sync();
-#ifndef SPARSE_MLA_EXPERIMENT_NO_SOFTMAX  // diagnostic build: barriers only, no softmax work
-      float s[64];
+      // Lane (head, low half) holds Q_lo . X_lo in columns 0-63, lane (head, high half) holds
+      // Q_hi . X_hi in columns 64-127 (the column address of a load is the same for the whole
+      // warp, so both ranges are read and each lane keeps its own). The two lanes of a head share
+      // the softmax work: the low lane owns tile rows 0-31, the high lane rows 32-63; each sends
+      // the partner the partial scores of the rows it does not own.
+      float first[32], second[32];  // this lane's partial scores of tile rows 0-31 and 32-63
 #pragma unroll
-      for (int c = 0; c < 64; c += 16)
-        tmem_ld16(s_addr + c, *reinterpret_cast<uint32_t(*)[16]>(&s[c]));
-      tmem_wait_ld();
-
-      // Add the partner half's partial product, scale, mask.
-      float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      for (int c = 0; c < 64; c += 16) {
+        uint32_t low[16], high[16];
+        tmem_ld16(s_addr + c, low);
+        tmem_ld16(s_addr + 64 + c, high);
+        tmem_wait_ld();
 #pragma unroll
-      for (int j = 0; j < 64; ++j) {
-        const float total = s[j] + __shfl_xor_sync(0xffffffffu, s[j], 16);
-        const bool live = ((j < 32 ? live_lo : live_hi) >> (j & 31)) & 1u;
-        s[j] = live ? total * p.scale_log2 : -INFINITY;
-        partial_max[j & 3] = fmaxf(partial_max[j & 3], s[j]);
+        for (int e = 0; e < 16; ++e) {
+          const float v = __uint_as_float(half ? high[e] : low[e]);
+          if (c < 32) first[c + e] = v; else second[c - 32 + e] = v;
+        }
       }
-      const float chunk_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3]));
+      // The scores are in registers: the next QK may overwrite the buffer.
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.bar(kSFree));
+
+      const unsigned live = half ? live_hi : live_lo;
+      float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      float mine[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float total = (half ? second[j] : first[j]) + __shfl_xor_sync(0xffffffffu, half ? first[j] : second[j], 16);
+        mine[j] = ((live >> j) & 1u) ? total * p.scale_log2 : -INFINITY;
+        partial_max[j & 3] = fmaxf(partial_max[j & 3], mine[j]);
+      }
+      float chunk_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3]));
+      chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, 16));
       // The running maximum only moves when it is exceeded by more than 8 (a factor 256), so the
       // accumulator is rescaled rarely; probabilities stay below 2^8 and all terms of one head
       // share the same reference, which cancels in the final division.
@@ -687,22 +737,25 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
           for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
           tmem_st16(tmem + kTmemO + c + lane_base, o);
         }
+        tmem_wait_st();
       }
       float partial_sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < 64; ++j) { s[j] = exp2f(s[j] - run_max); partial_sum[j & 3] += s[j]; }
+      for (int j = 0; j < 32; ++j) { mine[j] = exp2f(mine[j] - run_max); partial_sum[j & 3] += mine[j]; }
+      // `run_sum` is this lane's share of the denominator; the two shares meet in the epilogue.
       run_sum = run_sum * alpha + ((partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]));
 
-      // P as BF16 pairs over the start of this S buffer, in this thread's own lane half.
+      // P to shared memory, one 128-byte row per head; this lane writes its 32 rows (64 bytes).
+      // The tile was last read by the PV of two chunks ago, whose completion was observed below
+      // during the previous chunk.
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t packed[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) packed[e] = pack_pair<kFormat>(s[c * 32 + 2 * e], s[c * 32 + 2 * e + 1]);
-        tmem_st16(s_addr + c * 16, packed);
+      for (int u = 0; u < 4; ++u) {
+        uint4 v;
+        v.x = pack_pair<kFormat>(mine[8 * u + 0], mine[8 * u + 1]); v.y = pack_pair<kFormat>(mine[8 * u + 2], mine[8 * u + 3]);
+        v.z = pack_pair<kFormat>(mine[8 * u + 4], mine[8 * u + 5]); v.w = pack_pair<kFormat>(mine[8 * u + 6], mine[8 * u + 7]);
+        *reinterpret_cast<uint4*>(sm.ptr + kSmemStore + p_offset(buffer, head, half * 4 + u)) = v;
       }
-#endif
-      tmem_wait_st();
+      fence_proxy_async();  // the PV reads the tile through the async proxy
       tc_fence_before_sync();
       PROF_END(1);
       PROF_BEGIN;
@@ -729,7 +782,7 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
     PROF_END(3);
     PROF_BEGIN;
     if (threadIdx.x == 0) TRACE(sm, 23, token);
-    const float inverse = 1.f / run_sum;
+    const float inverse = 1.f / (run_sum + __shfl_xor_sync(0xffffffffu, run_sum, 16));
     // 64 columns per pass: tensor memory -> registers -> a swizzled per-warp staging tile ->
     // global, so that every store instruction writes four complete 128-byte lines.
     unsigned char* staging = sm.ptr + kSmemStore + warp * 4096;
@@ -790,7 +843,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
 
   if (threadIdx.x == 0) {
     const int P = kProducerWarps, S = kSoftmaxWarps, T = kProducerThreads;
-    const int counts[kBarCount] = {1, 1, S, S, P, 1, T, T, T, 1, 1, 1, 1, 1, S, S, 1, S};
+    const int counts[kBarCount] = {1, 1, S, S, P, 1, T, T, T, 1, 1, 1, 1, S, S, S, 1, S};
     for (int i = 0; i < kBarCount; ++i) mbar_init(sm.bar(i), counts[i]);
     mbar_fence_init();
     *sm.abort_flag() = 0;
