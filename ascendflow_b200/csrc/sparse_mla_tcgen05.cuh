@@ -94,9 +94,11 @@ struct TokenInfo {
 
 enum Bar {
   kTokenReady0 = 0, kTokenReady1, kTokenDone0, kTokenDone1, kQFull, kQFree,
-  kKvFull0, kKvFull1, kKvFull2, kKvFree0, kKvFree1, kKvFree2,
-  kSFull, kSFree, kPFull0, kPFull1, kODone, kOFree, kBarCount
+  kKvFree0, kKvFree1, kKvFree2,
+  kSFull, kSFree, kPFull0, kPFull1, kODone, kOFree,
+  kKvFull0, kKvFull1, kKvFull2, kBarCount
 };
+static_assert(kBarCount <= 32, "the barrier area holds 32 mbarriers");
 
 // Storage formats of kind::f16 instructions: 0 = IEEE half, 1 = BF16.
 template <int kFormat> constexpr uint32_t kIdescQK = idesc_f16(128, 128, kFormat, 0, 0);
@@ -429,13 +431,26 @@ __device__ void producer_role(const Params& p, const Shared& sm, uint32_t tmem) 
       PROF_BEGIN;
       if (tid == 0) TRACE(sm, 4, item);
       const uint32_t tile = sm.base + kSmemKv + stage * kTileBytes;
-      const int unit = tid & 63;
       const int chunk = info->chunk[item];
-      for (int r = tid >> 6; r < kChunkRows; r += kProducerThreads / 64) {
-        const int slot = chunk * kChunkRows + r;
+      // Sixteen threads per row and quarter: eight 16-byte units of block q, eight of block q + 4.
+      const int sub = tid & 15;
+      const char* source[kChunkRows / (kProducerThreads / 16)];
+      bool live[kChunkRows / (kProducerThreads / 16)];
+#pragma unroll
+      for (int k = 0; k < kChunkRows / (kProducerThreads / 16); ++k) {
+        const int slot = chunk * kChunkRows + (tid >> 4) + k * (kProducerThreads / 16);
         const int row = rows[slot];
-        const char* base = slot < kWindow ? window_base : compressed_base;
-        cp_async16(tile + swizzled(r, unit), base + (size_t)(row < 0 ? 0 : row) * kRowBytes + unit * 16, row >= 0);
+        live[k] = row >= 0;
+        source[k] = (slot < kWindow ? window_base : compressed_base) + (size_t)(row < 0 ? 0 : row) * kRowBytes;
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int unit = (q + 4 * (sub >> 3)) * 8 + (sub & 7);
+#pragma unroll
+        for (int k = 0; k < kChunkRows / (kProducerThreads / 16); ++k) {
+          const int r = (tid >> 4) + k * (kProducerThreads / 16);
+          cp_async16(tile + swizzled(r, unit), source[k] + unit * 16, live[k]);
+        }
       }
       cp_async_arrive(sm.bar(kKvFull0 + stage));
       PROF_END(2);
@@ -544,18 +559,28 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
     PROF_BEGIN;
     if (!mbar_wait(sm.bar(kQFull), working_tokens & 1, abort_flag)) return;
     PROF_END(1);
-    {  // first QK of the token
-      const uint32_t stage = chunk_count % kStages, use = chunk_count / kStages;
+    // QK of the chunk in ring slot `slot` (stage and phase follow from it). `landed` says that
+    // the tile has been seen to have landed already; `hook` runs a few MMAs before the end.
+    auto qk = [&](uint32_t slot, bool landed, auto&& hook) -> bool {
+      const uint32_t stage = slot % kStages, parity = (slot / kStages) & 1;
       PROF_BEGIN;
-      if (!mbar_wait(sm.bar(kKvFull0 + stage), use & 1, abort_flag)) return;
+      if (!landed && !mbar_wait(sm.bar(kKvFull0 + stage), parity, abort_flag)) return false;
+      PROF_END(2);
+      PROF_BEGIN;
+      issue_qk<kFormat, 0, 12>(sm, tmem, stage);
+      hook();
+      issue_qk<kFormat, 12, 16>(sm, tmem, stage);
+      PROF_END(3);
+      return true;
+    };
+    {  // first QK of the token
+      PROF_BEGIN;
       // the softmax warps have taken the previous chunk's scores out of the single buffer
       if (chunk_count > 0 && !mbar_wait(sm.bar(kSFree), (chunk_count - 1) & 1, abort_flag)) return;
-      PROF_END(2);
+      PROF_END(4);
       tc_fence_after_sync();
       TRACE(sm, 13, 0);
-      PROF_BEGIN;
-      issue_qk<kFormat>(sm, tmem, stage);
-      PROF_END(3);
+      if (!qk(chunk_count, false, [] {})) return;
       mma_commit(sm.bar(kSFull));
       if (chunks == 1) mma_commit(sm.bar(kQFree));
       TRACE(sm, 14, 0);
@@ -563,28 +588,21 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
     // The pipe's queue covers only ~150 cycles, so nothing slow may sit between the last QK MMA
     // of a chunk and the first PV MMA: barriers are tested (without blocking) a few MMAs before
     // they are needed, and waited on only if that failed.
-    constexpr int kQkTail = 4;  // QK MMAs issued after the early test of the P barrier
-    bool kv_ready = false;      // the tile of the next QK has already been seen to have landed
+    bool kv_ready = false;      // the first quarter of the next QK's tile has been seen to have landed
     for (int i = 0; i < chunks; ++i, ++chunk_count) {
       const uint32_t c = chunk_count, stage = c % kStages;
       bool p_ready = false;
       if (i + 1 < chunks) {  // QK of the next chunk runs while the softmax warps work on this one
-        const uint32_t next = c + 1, next_stage = next % kStages, use = next / kStages;
-        PROF_BEGIN;
-        if (!kv_ready && !mbar_wait(sm.bar(kKvFull0 + next_stage), use & 1, abort_flag)) return;
-        PROF_END(2);
         PROF_BEGIN;
         // The score buffer is free once the softmax warps have read chunk c out of it.
         if (!mbar_wait(sm.bar(kSFree), c & 1, abort_flag)) return;
         PROF_END(4);
         tc_fence_after_sync();
         TRACE(sm, 13, i + 1);
-        PROF_BEGIN;
-        issue_qk<kFormat, 0, kQkSteps - kQkTail>(sm, tmem, next_stage);
-        if (i > 0) p_ready = mbar_test(sm.bar(kPFull0 + (c & 1)), (c >> 1) & 1);
-        if (p_ready) tc_fence_after_sync();
-        issue_qk<kFormat, kQkSteps - kQkTail, kQkSteps>(sm, tmem, next_stage);
-        PROF_END(3);
+        if (!qk(c + 1, kv_ready, [&] {
+              if (i > 0) p_ready = mbar_test(sm.bar(kPFull0 + (c & 1)), (c >> 1) & 1);
+              if (p_ready) tc_fence_after_sync();
+            })) return;
         mma_commit(sm.bar(kSFull));
         if (i + 2 == chunks) mma_commit(sm.bar(kQFree));
         TRACE(sm, 14, i + 1);
@@ -592,7 +610,7 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
       if (i == 0) {  // the previous token's epilogue must have read O
         PROF_BEGIN;
         if (!mbar_wait(sm.bar(kOFree), (working_tokens & 1) ^ 1, abort_flag)) return;
-        PROF_END(4);
+        PROF_END(1);
       }
       TRACE(sm, 10, i);
       if (!p_ready) {
@@ -843,7 +861,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
 
   if (threadIdx.x == 0) {
     const int P = kProducerWarps, S = kSoftmaxWarps, T = kProducerThreads;
-    const int counts[kBarCount] = {1, 1, S, S, P, 1, T, T, T, 1, 1, 1, 1, S, S, S, 1, S};
+    const int counts[kBarCount] = {1, 1, S, S, P, 1, 1, 1, 1, 1, S, S, S, 1, S, T, T, T};
     for (int i = 0; i < kBarCount; ++i) mbar_init(sm.bar(i), counts[i]);
     mbar_fence_init();
     *sm.abort_flag() = 0;
