@@ -63,10 +63,11 @@ constexpr int kTileBytes = 8 * kBlockBytes;                 // 64 rows x 512 fea
 
 // Shared memory map (bytes from a 1024-aligned base).
 constexpr int kSmemKv = 0;
-// Per softmax warp 4 KiB: the epilogue's 32 x 128-byte staging rows. The same bytes hold the two
-// P tiles between epilogues (see `p_offset`): a warp only ever touches its own 4 KiB of either.
-// 1024-byte aligned like the tiles, because the swizzle is a function of the address.
-constexpr int kSmemStore = kSmemKv + kStages * kTileBytes;
+// The P tile (64 heads x 64 rows, 8 KiB) and, per softmax warp, 4 KiB of epilogue staging
+// (32 x 128-byte rows). Both 1024-byte aligned like the tiles, because the swizzle is a function
+// of the address.
+constexpr int kSmemP = kSmemKv + kStages * kTileBytes;
+constexpr int kSmemStore = kSmemP + kHeads * 128;
 constexpr int kSmemRows = kSmemStore + kSoftmaxWarps * 4096;   // int[2][640]
 constexpr int kSmemInfo = kSmemRows + 2 * kSlots * 4;       // TokenInfo[2]
 constexpr int kSmemBars = kSmemInfo + 2 * 64;               // mbarriers
@@ -95,7 +96,7 @@ struct TokenInfo {
 enum Bar {
   kTokenReady0 = 0, kTokenReady1, kTokenDone0, kTokenDone1, kQFull, kQFree,
   kKvFree0, kKvFree1, kKvFree2,
-  kSFull, kSFree, kPFull0, kPFull1, kODone, kOFree,
+  kSFull, kSFree, kPFull, kODone, kOFree,
   kKvFull0, kKvFull1, kKvFull2, kBarCount
 };
 static_assert(kBarCount <= 32, "the barrier area holds 32 mbarriers");
@@ -115,13 +116,10 @@ __device__ __forceinline__ uint32_t swizzled(int row, int unit) {
   return block_position(unit >> 3) * kBlockBytes + row * 128 + (((unit & 7) ^ (row & 7)) << 4);
 }
 
-// P tile `buffer` (64 heads x 64 rows of 16-bit probabilities, K-major, 128-byte swizzle: one
-// 128-byte row per head): byte offset of 16-byte unit `unit` (0..7) of head `head` from
-// kSmemStore. Eight-head groups are 2048 bytes apart and the two buffers interleave at 1024, so
-// the heads 16 w .. 16 w + 15 of softmax warp w lie inside that warp's own 4 KiB.
-constexpr int kPGroupBytes = 2048;
-__device__ __forceinline__ uint32_t p_offset(int buffer, int head, int unit) {
-  return (head >> 3) * kPGroupBytes + buffer * 1024 + (head & 7) * 128 + ((unit ^ (head & 7)) << 4);
+// The P tile (64 heads x 64 rows of 16-bit probabilities, K-major, 128-byte swizzle: one
+// 128-byte row per head): byte offset of 16-byte unit `unit` (0..7) of head `head` from kSmemP.
+__device__ __forceinline__ uint32_t p_offset(int head, int unit) {
+  return head * 128 + ((unit ^ (head & 7)) << 4);
 }
 
 struct Shared {
@@ -534,9 +532,9 @@ __device__ __forceinline__ void issue_pv_steps(uint32_t o_tmem, uint64_t p_desc,
 // features contiguous: the four 64-feature blocks of a half are two block positions apart,
 // 8-row groups 1024 bytes apart.
 template <int kFormat>
-__device__ __forceinline__ void issue_pv(const Shared& sm, uint32_t tmem, int stage, int buffer, bool accumulate) {
+__device__ __forceinline__ void issue_pv(const Shared& sm, uint32_t tmem, int stage, bool accumulate) {
   const uint64_t x_desc = smem_desc_sw128(sm.base + kSmemKv + stage * kTileBytes, 2 * kBlockBytes, 1024);
-  const uint64_t p_desc = smem_desc_sw128(sm.base + kSmemStore + buffer * 1024, 16, kPGroupBytes);
+  const uint64_t p_desc = smem_desc_sw128(sm.base + kSmemP, 16, 1024);
   if (accumulate) issue_pv_steps<kFormat, 0, false>(tmem + kTmemO, p_desc, x_desc);
   else issue_pv_steps<kFormat, 0, true>(tmem + kTmemO, p_desc, x_desc);
 }
@@ -546,9 +544,42 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
   volatile int* abort_flag = sm.abort_flag();
   PROF_DECL;
   const long long prof_start_ = clock64(); (void)prof_start_;
-  // `chunk_count` counts chunks over all tokens: chunk c uses ring stage c % kStages, P tile
-  // c & 1, and the c-th phase of the score barriers.
+  // The chunks of all working tokens form one stream: chunk c uses ring stage c % kStages and the
+  // c-th phase of the score and P barriers. The issue order is QK(c + 1), PV(c) throughout, also
+  // across a token boundary: the first QK of a token is issued before the last PV of the
+  // previous one, so that the softmax warps always have scores to work on.
   uint32_t chunk_count = 0, token_count = 0, working_tokens = 0;
+  bool pending = false;        // a chunk whose QK has been issued and whose PV has not
+  bool pending_first = false;  // it is the first chunk of its token (PV overwrites O)
+  uint32_t pending_token = 0;  // index of its token among the working tokens
+  bool p_ready = false;        // its P has been seen to be complete
+
+  // PV of the pending chunk c. Returns false on a failed wait.
+  auto pv = [&](uint32_t c) -> bool {
+    if (pending_first) {  // the previous token's epilogue must have read O
+      PROF_BEGIN;
+      if (!mbar_wait(sm.bar(kOFree), (pending_token & 1) ^ 1, abort_flag)) return false;
+      PROF_END(1);
+      tc_fence_after_sync();
+    }
+    TRACE(sm, 10, c);
+    if (!p_ready) {
+      PROF_BEGIN;
+      if (!mbar_wait(sm.bar(kPFull), c & 1, abort_flag)) return false;
+      PROF_END(5);
+      tc_fence_after_sync();
+    }
+    TRACE(sm, 11, c);
+    PROF_BEGIN;
+    issue_pv<kFormat>(sm, tmem, c % kStages, !pending_first);
+    PROF_END(6);
+    mma_commit(sm.bar(kKvFree0 + c % kStages));
+    mma_commit(sm.bar(kODone));
+    TRACE(sm, 12, c);
+    pending = false;
+    return true;
+  };
+
   TokenWalk walk(p);
   for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
     PROF_BEGIN;
@@ -556,85 +587,43 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
     PROF_END(0);
     const int chunks = sm.info(token_count & 1)->chunks;
     if (chunks == 0) continue;
-    PROF_BEGIN;
-    if (!mbar_wait(sm.bar(kQFull), working_tokens & 1, abort_flag)) return;
-    PROF_END(1);
-    // QK of the chunk in ring slot `slot` (stage and phase follow from it). `landed` says that
-    // the tile has been seen to have landed already; `hook` runs a few MMAs before the end.
-    auto qk = [&](uint32_t slot, bool landed, auto&& hook) -> bool {
-      const uint32_t stage = slot % kStages, parity = (slot / kStages) & 1;
-      PROF_BEGIN;
-      if (!landed && !mbar_wait(sm.bar(kKvFull0 + stage), parity, abort_flag)) return false;
-      PROF_END(2);
-      PROF_BEGIN;
-      issue_qk<kFormat, 0, 12>(sm, tmem, stage);
-      hook();
-      issue_qk<kFormat, 12, 16>(sm, tmem, stage);
-      PROF_END(3);
-      return true;
-    };
-    {  // first QK of the token
-      PROF_BEGIN;
-      // the softmax warps have taken the previous chunk's scores out of the single buffer
-      if (chunk_count > 0 && !mbar_wait(sm.bar(kSFree), (chunk_count - 1) & 1, abort_flag)) return;
-      PROF_END(4);
-      tc_fence_after_sync();
-      TRACE(sm, 13, 0);
-      if (!qk(chunk_count, false, [] {})) return;
-      mma_commit(sm.bar(kSFull));
-      if (chunks == 1) mma_commit(sm.bar(kQFree));
-      TRACE(sm, 14, 0);
-    }
-    // The pipe's queue covers only ~150 cycles, so nothing slow may sit between the last QK MMA
-    // of a chunk and the first PV MMA: barriers are tested (without blocking) a few MMAs before
-    // they are needed, and waited on only if that failed.
-    bool kv_ready = false;      // the first quarter of the next QK's tile has been seen to have landed
-    for (int i = 0; i < chunks; ++i, ++chunk_count) {
+    for (int i = 0; i < chunks; ++i) {
       const uint32_t c = chunk_count, stage = c % kStages;
-      bool p_ready = false;
-      if (i + 1 < chunks) {  // QK of the next chunk runs while the softmax warps work on this one
+      if (i == 0) {  // the token's Q is in tensor memory
         PROF_BEGIN;
-        // The score buffer is free once the softmax warps have read chunk c out of it.
-        if (!mbar_wait(sm.bar(kSFree), c & 1, abort_flag)) return;
-        PROF_END(4);
-        tc_fence_after_sync();
-        TRACE(sm, 13, i + 1);
-        if (!qk(c + 1, kv_ready, [&] {
-              if (i > 0) p_ready = mbar_test(sm.bar(kPFull0 + (c & 1)), (c >> 1) & 1);
-              if (p_ready) tc_fence_after_sync();
-            })) return;
-        mma_commit(sm.bar(kSFull));
-        if (i + 2 == chunks) mma_commit(sm.bar(kQFree));
-        TRACE(sm, 14, i + 1);
-      }
-      if (i == 0) {  // the previous token's epilogue must have read O
-        PROF_BEGIN;
-        if (!mbar_wait(sm.bar(kOFree), (working_tokens & 1) ^ 1, abort_flag)) return;
+        if (!mbar_wait(sm.bar(kQFull), working_tokens & 1, abort_flag)) return;
         PROF_END(1);
       }
-      TRACE(sm, 10, i);
-      if (!p_ready) {
-        PROF_BEGIN;
-        if (!mbar_wait(sm.bar(kPFull0 + (c & 1)), (c >> 1) & 1, abort_flag)) return;
-        PROF_END(5);
-        tc_fence_after_sync();
-      }
-      // Look at the tile of the QK that follows this PV now, so that no wait separates them.
-      kv_ready = false;
-      if (i + 2 < chunks) {
-        const uint32_t n = c + 2;
-        kv_ready = mbar_test(sm.bar(kKvFull0 + n % kStages), (n / kStages) & 1);
-      }
-      TRACE(sm, 11, i);
       PROF_BEGIN;
-      issue_pv<kFormat>(sm, tmem, stage, c & 1, i > 0);
-      PROF_END(6);
-      mma_commit(sm.bar(kKvFree0 + stage));
-      mma_commit(sm.bar(kODone));
-      TRACE(sm, 12, i);
+      if (!mbar_wait(sm.bar(kKvFull0 + stage), (c / kStages) & 1, abort_flag)) return;
+      PROF_END(2);
+      PROF_BEGIN;
+      // The single score buffer is free once the softmax warps have read chunk c - 1 out of it.
+      if (c > 0 && !mbar_wait(sm.bar(kSFree), (c - 1) & 1, abort_flag)) return;
+      PROF_END(4);
+      tc_fence_after_sync();
+      TRACE(sm, 13, c);
+      PROF_BEGIN;
+      // The pipe's queue covers only ~150 cycles, so nothing slow may sit between the last QK
+      // MMA and the first PV MMA: the P barrier is tested (without blocking) a few MMAs early
+      // and waited on only if that failed.
+      issue_qk<kFormat, 0, 12>(sm, tmem, stage);
+      p_ready = pending && mbar_test(sm.bar(kPFull), (c - 1) & 1);
+      if (p_ready) tc_fence_after_sync();
+      issue_qk<kFormat, 12, 16>(sm, tmem, stage);
+      PROF_END(3);
+      mma_commit(sm.bar(kSFull));
+      if (i + 1 == chunks) mma_commit(sm.bar(kQFree));  // the last QK that reads this token's Q
+      TRACE(sm, 14, c);
+      if (pending && !pv(c - 1)) return;
+      pending = true;
+      pending_first = i == 0;
+      pending_token = working_tokens;
+      ++chunk_count;
     }
     ++working_tokens;
   }
+  if (pending) { p_ready = false; if (!pv(chunk_count - 1)) return; }
 #ifdef SPARSE_MLA_PROFILE
   prof_[7] = clock64() - prof_start_;
 #endif
@@ -666,6 +655,73 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   const float sink = __ldg(p.sinks + head) * 1.4426950408889634f;  // log2 domain
   uint32_t chunk_count = 0, token_count = 0, pv_waited = 0;
   __nv_bfloat16* out_base = static_cast<__nv_bfloat16*>(p.out);
+  const uint32_t s_addr = tmem + kTmemS + lane_base;
+
+  // PVs complete in order: wait until those of chunks 0 .. upto - 1 have.
+  auto wait_pv = [&](uint32_t upto) -> bool {
+    while (pv_waited < upto) {
+      if (!warp_wait(sm.bar(kODone), pv_waited & 1, abort_flag)) return false;
+      ++pv_waited;
+    }
+    return true;
+  };
+
+  // A finished token waits for its epilogue until the first chunk of the next working token has
+  // been through the softmax, so that the MMA thread has a P to go on with while O is written out.
+  int done_token = -1;          // token whose O is complete (or about to be) and not yet stored
+  uint32_t done_count = 0;      // its index in this block's walk
+  float done_sum = 0.f;         // this lane's share of its denominator
+
+  // O / denominator -> 16-bit -> global for `done_token`: 64 columns per pass, tensor memory ->
+  // registers -> a swizzled per-warp staging tile -> global, so that every store instruction
+  // writes four complete 128-byte lines.
+  auto epilogue = [&]() -> bool {
+    PROF_BEGIN;
+    if (!wait_pv(chunk_count)) return false;  // its last PV
+    tc_fence_after_sync();
+    PROF_END(3);
+    PROF_BEGIN;
+    if (threadIdx.x == 0) TRACE(sm, 23, done_token);
+    const float inverse = 1.f / (done_sum + __shfl_xor_sync(0xffffffffu, done_sum, 16));
+    unsigned char* staging = sm.ptr + kSmemStore + warp * 4096;
+    __nv_bfloat16* token_out = out_base + (size_t)done_token * kHeads * kFeatures;
+#pragma unroll 1
+    for (int c = 0; c < 256; c += 64) {
+      uint32_t o[64];
+#pragma unroll
+      for (int q = 0; q < 64; q += 16)
+        tmem_ld16(tmem + kTmemO + c + q + lane_base, *reinterpret_cast<uint32_t(*)[16]>(&o[q]));
+      tmem_wait_ld();
+#pragma unroll
+      for (int unit = 0; unit < 8; ++unit) {
+        uint4 v;
+        v.x = pack_pair<kFormat>(__uint_as_float(o[unit * 8 + 0]) * inverse, __uint_as_float(o[unit * 8 + 1]) * inverse);
+        v.y = pack_pair<kFormat>(__uint_as_float(o[unit * 8 + 2]) * inverse, __uint_as_float(o[unit * 8 + 3]) * inverse);
+        v.z = pack_pair<kFormat>(__uint_as_float(o[unit * 8 + 4]) * inverse, __uint_as_float(o[unit * 8 + 5]) * inverse);
+        v.w = pack_pair<kFormat>(__uint_as_float(o[unit * 8 + 6]) * inverse, __uint_as_float(o[unit * 8 + 7]) * inverse);
+        *reinterpret_cast<uint4*>(staging + lane * 128 + ((unit ^ (lane & 7)) << 4)) = v;
+      }
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = i * 4 + (lane >> 3), unit = lane & 7;  // staging row = owning lane
+        const uint4 v = *reinterpret_cast<const uint4*>(staging + row * 128 + ((unit ^ (row & 7)) << 4));
+        __nv_bfloat16* dst = token_out + (size_t)(warp * 16 + (row & 15)) * kFeatures + (row >> 4) * 256 + c + unit * 8;
+        *reinterpret_cast<uint4*>(dst) = v;
+      }
+      __syncwarp();
+    }
+    tc_fence_before_sync();
+    __syncwarp();
+    PROF_END(4);
+    if (threadIdx.x == 0) TRACE(sm, 24, done_token);
+    if (lane == 0) {
+      mbar_arrive(sm.bar(kOFree));
+      mbar_arrive(sm.bar(kTokenDone0 + (done_count & 1)));
+    }
+    done_token = -1;
+    return true;
+  };
 
   TokenWalk walk(p);
   for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
@@ -673,8 +729,11 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
     const TokenInfo* info = sm.info(token_count & 1);
     const int* rows = sm.rows(token_count & 1);
     const int chunks = info->chunks;
-    __nv_bfloat16* out = out_base + ((size_t)token * kHeads + head) * kFeatures + half * 256;
     if (chunks == 0) {  // nothing visible: the output row is zero whatever the sink
+      // The resolver needs the finished token's row buffer back before it can publish the token
+      // after this one: no point in holding its epilogue any longer.
+      if (done_token >= 0 && !epilogue()) return;
+      __nv_bfloat16* out = out_base + ((size_t)token * kHeads + head) * kFeatures + half * 256;
       for (int i = 0; i < 256; i += 8) *reinterpret_cast<uint4*>(out + i) = make_uint4(0, 0, 0, 0);
       __syncwarp();
       if (lane == 0) mbar_arrive(sm.bar(kTokenDone0 + (token_count & 1)));
@@ -684,18 +743,16 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
     // sink's own weight exp2(sink - run_max) = 1.
     float run_max = sink, run_sum = half ? 0.f : 1.f;
     for (int i = 0; i < chunks; ++i, ++chunk_count) {
-      const uint32_t buffer = chunk_count & 1;
       const int chunk = info->chunk[i];
       const unsigned live_lo = __ballot_sync(0xffffffffu, rows[chunk * kChunkRows + lane] >= 0);
       const unsigned live_hi = __ballot_sync(0xffffffffu, rows[chunk * kChunkRows + 32 + lane] >= 0);
-      const uint32_t s_addr = tmem + kTmemS + lane_base;
 
-      if (threadIdx.x == 0) TRACE(sm, 20, i);
+      if (threadIdx.x == 0) TRACE(sm, 20, chunk_count);
       PROF_BEGIN;
       if (!warp_wait(sm.bar(kSFull), chunk_count & 1, abort_flag)) return;
       PROF_END(0);
       PROF_BEGIN;
-      if (threadIdx.x == 0) TRACE(sm, 21, i);
+      if (threadIdx.x == 0) TRACE(sm, 21, chunk_count);
       tc_fence_after_sync();
       // Lane (head, low half) holds Q_lo . X_lo in columns 0-63, lane (head, high half) holds
       // Q_hi . X_hi in columns 64-127 (the column address of a load is the same for the whole
@@ -741,10 +798,7 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       }
       if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
         // O holds earlier chunks: the previous PV must have landed before it is rescaled.
-        while (pv_waited < chunk_count) {
-          if (!warp_wait(sm.bar(kODone), pv_waited & 1, abort_flag)) return;
-          ++pv_waited;
-        }
+        if (!wait_pv(chunk_count)) return;
         tc_fence_after_sync();
 #pragma unroll 1
         for (int c = 0; c < 256; c += 16) {
@@ -760,86 +814,34 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       float partial_sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < 32; ++j) { mine[j] = exp2f(mine[j] - run_max); partial_sum[j & 3] += mine[j]; }
-      // `run_sum` is this lane's share of the denominator; the two shares meet in the epilogue.
       run_sum = run_sum * alpha + ((partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]));
-
+      PROF_END(1);
+      PROF_BEGIN;
+      // There is one P tile: the previous chunk's PV must have finished reading it. (In step, that
+      // PV ran right behind the QK whose scores this chunk started from.)
+      if (!wait_pv(chunk_count)) return;
+      PROF_END(2);
       // P to shared memory, one 128-byte row per head; this lane writes its 32 rows (64 bytes).
-      // The tile was last read by the PV of two chunks ago, whose completion was observed below
-      // during the previous chunk.
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         uint4 v;
         v.x = pack_pair<kFormat>(mine[8 * u + 0], mine[8 * u + 1]); v.y = pack_pair<kFormat>(mine[8 * u + 2], mine[8 * u + 3]);
         v.z = pack_pair<kFormat>(mine[8 * u + 4], mine[8 * u + 5]); v.w = pack_pair<kFormat>(mine[8 * u + 6], mine[8 * u + 7]);
-        *reinterpret_cast<uint4*>(sm.ptr + kSmemStore + p_offset(buffer, head, half * 4 + u)) = v;
+        *reinterpret_cast<uint4*>(sm.ptr + kSmemP + p_offset(head, half * 4 + u)) = v;
       }
       fence_proxy_async();  // the PV reads the tile through the async proxy
       tc_fence_before_sync();
-      PROF_END(1);
-      PROF_BEGIN;
-      // Observe the previous chunk's PV completion before releasing this P: the PV barrier then
-      // never runs more than one phase ahead of this warp.
-      while (pv_waited < chunk_count) {
-        if (!warp_wait(sm.bar(kODone), pv_waited & 1, abort_flag)) return;
-        ++pv_waited;
-      }
       __syncwarp();
-      PROF_END(2);
-      if (threadIdx.x == 0) TRACE(sm, 22, i);
-      if (lane == 0) mbar_arrive(sm.bar(kPFull0 + buffer));
+      if (threadIdx.x == 0) TRACE(sm, 22, chunk_count);
+      if (lane == 0) mbar_arrive(sm.bar(kPFull));
+      // The previous token's output, now that the MMA thread has this token's first P to go on with.
+      if (done_token >= 0 && !epilogue()) return;
     }
-
-    PROF_BEGIN;
-
-    // ---- epilogue: O / denominator -> BF16 -> global ------------------------------------------
-    while (pv_waited < chunk_count) {
-      if (!warp_wait(sm.bar(kODone), pv_waited & 1, abort_flag)) return;
-      ++pv_waited;
-    }
-    tc_fence_after_sync();
-    PROF_END(3);
-    PROF_BEGIN;
-    if (threadIdx.x == 0) TRACE(sm, 23, token);
-    const float inverse = 1.f / (run_sum + __shfl_xor_sync(0xffffffffu, run_sum, 16));
-    // 64 columns per pass: tensor memory -> registers -> a swizzled per-warp staging tile ->
-    // global, so that every store instruction writes four complete 128-byte lines.
-    unsigned char* staging = sm.ptr + kSmemStore + warp * 4096;
-    __nv_bfloat16* token_out = out_base + (size_t)token * kHeads * kFeatures;
-#pragma unroll 1
-    for (int c = 0; c < 256; c += 64) {
-      uint32_t o[64];
-#pragma unroll
-      for (int q = 0; q < 64; q += 16)
-        tmem_ld16(tmem + kTmemO + c + q + lane_base, *reinterpret_cast<uint32_t(*)[16]>(&o[q]));
-      tmem_wait_ld();
-#pragma unroll
-      for (int unit = 0; unit < 8; ++unit) {
-        uint4 v;
-        v.x = pack_pair<kFormat>(__uint_as_float(o[unit * 8 + 0]) * inverse, __uint_as_float(o[unit * 8 + 1]) * inverse);
-        v.y = pack_pair<kFormat>(__uint_as_float(o[unit * 8 + 2]) * inverse, __uint_as_float(o[unit * 8 + 3]) * inverse);
-        v.z = pack_pair<kFormat>(__uint_as_float(o[unit * 8 + 4]) * inverse, __uint_as_float(o[unit * 8 + 5]) * inverse);
-        v.w = pack_pair<kFormat>(__uint_as_float(o[unit * 8 + 6]) * inverse, __uint_as_float(o[unit * 8 + 7]) * inverse);
-        *reinterpret_cast<uint4*>(staging + lane * 128 + ((unit ^ (lane & 7)) << 4)) = v;
-      }
-      __syncwarp();
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int row = i * 4 + (lane >> 3), unit = lane & 7;  // staging row = owning lane
-        const uint4 v = *reinterpret_cast<const uint4*>(staging + row * 128 + ((unit ^ (row & 7)) << 4));
-        __nv_bfloat16* dst = token_out + (size_t)(warp * 16 + (row & 15)) * kFeatures + (row >> 4) * 256 + c + unit * 8;
-        *reinterpret_cast<uint4*>(dst) = v;
-      }
-      __syncwarp();
-    }
-    tc_fence_before_sync();
-    __syncwarp();
-    PROF_END(4);
-    if (threadIdx.x == 0) TRACE(sm, 24, token);
-    if (lane == 0) {
-      mbar_arrive(sm.bar(kOFree));
-      mbar_arrive(sm.bar(kTokenDone0 + (token_count & 1)));
-    }
+    done_token = token;
+    done_count = token_count;
+    done_sum = run_sum;
   }
+  if (done_token >= 0 && !epilogue()) return;
 #ifdef SPARSE_MLA_PROFILE
   prof_[7] = clock64() - prof_start_;
 #endif
@@ -861,7 +863,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
 
   if (threadIdx.x == 0) {
     const int P = kProducerWarps, S = kSoftmaxWarps, T = kProducerThreads;
-    const int counts[kBarCount] = {1, 1, S, S, P, 1, 1, 1, 1, 1, S, S, S, 1, S, T, T, T};
+    const int counts[kBarCount] = {1, 1, S, S, P, 1, 1, 1, 1, 1, S, S, 1, S, T, T, T};
     for (int i = 0; i < kBarCount; ++i) mbar_init(sm.bar(i), counts[i]);
     mbar_fence_init();
     *sm.abort_flag() = 0;
