@@ -74,7 +74,7 @@ constexpr int kSmemBars = kSmemInfo + 2 * 64;               // mbarriers
 constexpr int kSmemMisc = kSmemBars + 32 * 8;               // tmem slot, abort flag
 constexpr int kSmemEnd = kSmemMisc + 64;
 #ifdef SPARSE_MLA_TRACE
-constexpr int kTraceEntries = 900;
+constexpr int kTraceEntries = 540;
 constexpr int kSmemTrace = kSmemEnd;
 constexpr int kSmemBytes = kSmemTrace + 16 + kTraceEntries * 8 + 1024;
 #else
@@ -166,7 +166,7 @@ __device__ __forceinline__ void trace(const Shared& sm, int event, int value) {
   if (blockIdx.x != 0) return;
   const int role = threadIdx.x == 0 ? 2 : (threadIdx.x == kMmaWarp * 32 ? 1 : 0);
   unsigned* log = reinterpret_cast<unsigned*>(sm.ptr + kSmemTrace);
-  const unsigned slot = log[role]++;
+  const unsigned slot = role == 0 ? atomicAdd(&log[0], 1u) : log[role]++;  // several producer threads may log
   constexpr unsigned per_role = kTraceEntries / 3;
   if (slot < per_role) {
     log[4 + 2 * (role * per_role + slot)] = (unsigned(event) << 24) | (unsigned(value) & 0xffffffu);
@@ -580,13 +580,27 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
     return true;
   };
 
-  TokenWalk walk(p);
-  for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
+  // This thread needs the number of tokens only (the resolver publishes each token's chunk count):
+  // the walk's divisions would sit on the critical path between two tokens.
+  uint32_t my_tokens = 0;
+  {
+    TokenWalk walk(p);
+    while (walk.next() >= 0) ++my_tokens;
+  }
+  for (; token_count < my_tokens; ++token_count) {
+    // The pending PV normally goes out behind the next token's first QK. If that token is not
+    // there yet, or has no work, it must not be held back: the previous token's epilogue waits
+    // for it, and the publication of later tokens waits for that epilogue.
+    const uint32_t ready = sm.bar(kTokenReady0 + (token_count & 1)), ready_parity = (token_count >> 1) & 1;
+    if (pending && !mbar_test(ready, ready_parity)) { p_ready = false; if (!pv(chunk_count - 1)) return; }
     PROF_BEGIN;
-    if (!mbar_wait(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
+    if (!mbar_wait(ready, ready_parity, abort_flag)) return;
     PROF_END(0);
     const int chunks = sm.info(token_count & 1)->chunks;
-    if (chunks == 0) continue;
+    if (chunks == 0) {
+      if (pending) { p_ready = false; if (!pv(chunk_count - 1)) return; }
+      continue;
+    }
     for (int i = 0; i < chunks; ++i) {
       const uint32_t c = chunk_count, stage = c % kStages;
       if (i == 0) {  // the token's Q is in tensor memory
@@ -692,6 +706,11 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       for (int q = 0; q < 64; q += 16)
         tmem_ld16(tmem + kTmemO + c + q + lane_base, *reinterpret_cast<uint32_t(*)[16]>(&o[q]));
       tmem_wait_ld();
+      if (c == 192) {  // O has been read completely: the next token's first PV may overwrite it
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.bar(kOFree));
+      }
 #pragma unroll
       for (int unit = 0; unit < 8; ++unit) {
         uint4 v;
@@ -711,14 +730,9 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       }
       __syncwarp();
     }
-    tc_fence_before_sync();
-    __syncwarp();
     PROF_END(4);
     if (threadIdx.x == 0) TRACE(sm, 24, done_token);
-    if (lane == 0) {
-      mbar_arrive(sm.bar(kOFree));
-      mbar_arrive(sm.bar(kTokenDone0 + (done_count & 1)));
-    }
+    if (lane == 0) mbar_arrive(sm.bar(kTokenDone0 + (done_count & 1)));
     done_token = -1;
     return true;
   };

@@ -242,6 +242,38 @@ def test_randomised_requests(ops, seed):
     S.assert_close(actual, O.reference_fp32_from_data(data, policy), f"seed {seed}")
 
 
+def test_blocks_walk_through_empty_and_short_tokens(ops):
+    """More tokens than blocks, so that one persistent block meets, in turn, a full token, a token
+    with nothing visible, another full one and tokens of one or two chunks: the roles hand work
+    across token boundaries and must neither stall (status word) nor mix tokens up."""
+    sms = 148
+    lens = [sms, 2 * sms, sms + 52]           # block b gets tokens b, b + 148, b + 296, b + 444, ...
+    policy = O.make_policy(len(lens), sum(lens), ratio=2, max_seq=4096, blocks=128)
+    data = O.validation_inputs(policy, "mixed", lens)
+    # Request 1 holds half as many cached rows as it has queries: its first 148 tokens see nothing.
+    # Request 2 holds exactly its queries: token j sees j + 1 window rows (one or two chunks) and
+    # (j + 1) // 2 compressed rows.
+    lengths = np.array([2048, sms, lens[2]], dtype=np.int32)
+    data["seqused_ori_kv"] = lengths
+    data["seqused_cmp_kv"] = (lengths // 2).astype(np.int32)
+    data["cmp_residual_kv"] = (lengths % 2).astype(np.int32)
+    rng = np.random.default_rng(77)
+    for token in range(policy["T"]):
+        count = int(rng.integers(0, 513))
+        row = np.full(512, -1, dtype=np.int32)
+        row[:count] = rng.integers(0, 1024, count)
+        data["cmp_sparse_indices"][token, 0] = row
+    tensors, buffers = S.to_device(data, policy)
+    binding = ops.kernel("sparse_mla")(*(tensors[name] for name in S.TENSOR_ORDER))
+    assert binding.status()[0] == 0
+    rows = O.resolve_rows(data, policy)
+    live = (rows >= 0).sum(axis=1)
+    assert (live[sms:2 * sms] == 0).all() and (live[:sms] > 0).all() and (live[2 * sms:3 * sms] > 0).all()
+    actual = S.output_to_numpy(tensors["attention_out"], "bf16")
+    assert not actual[sms:2 * sms].any()
+    S.assert_close(actual, O.reference_fp32_from_data(data, policy), "empty and short tokens")
+
+
 def test_gather_experiment_rows_are_bit_exact():
     """The isolated gather experiment (counterpart of the reference's gather study) checks its rows."""
     from ascendflow_b200 import gather_bench
