@@ -96,7 +96,7 @@ struct TokenInfo {
 enum Bar {
   kTokenReady0 = 0, kTokenReady1, kTokenDone0, kTokenDone1, kQFull, kQFree,
   kKvFree0, kKvFree1, kKvFree2,
-  kSFull, kSFree, kPFull, kODone, kOFree,
+  kSFull, kPFull, kOFree,
   kKvFull0, kKvFull1, kKvFull2, kBarCount
 };
 static_assert(kBarCount <= 32, "the barrier area holds 32 mbarriers");
@@ -163,6 +163,9 @@ struct TokenWalk {
 // Three private logs (producer thread 0, MMA thread, softmax thread 0), each kTraceEntries / 3
 // entries of (event << 24 | value, clock); word 0..2 of the region hold the three counts.
 __device__ __forceinline__ void trace(const Shared& sm, int event, int value) {
+#ifdef SPARSE_MLA_TRACE_ONLY  // bit mask of the events to keep, so that logging does not stretch the timeline
+  if (!((SPARSE_MLA_TRACE_ONLY >> event) & 1)) return;
+#endif
   if (blockIdx.x != 0) return;
   const int role = threadIdx.x == 0 ? 2 : (threadIdx.x == kMmaWarp * 32 ? 1 : 0);
   unsigned* log = reinterpret_cast<unsigned*>(sm.ptr + kSmemTrace);
@@ -516,14 +519,15 @@ __device__ __forceinline__ void issue_qk(const Shared& sm, uint32_t tmem, int st
   issue_qk_steps<kFormat, kBegin, kEnd>(tmem + kTmemS, tmem + kTmemQ, x_desc);
 }
 
-template <int kFormat, int I, bool kFirst>
+constexpr int kPvSteps = 2 * (kChunkRows / 16);
+template <int kFormat, int I, bool kFirst, int kEnd = kPvSteps>
 __device__ __forceinline__ void issue_pv_steps(uint32_t o_tmem, uint64_t p_desc, uint64_t x_desc) {
-  if constexpr (I < 2 * (kChunkRows / 16)) {
+  if constexpr (I < kEnd) {
     constexpr int h = I / (kChunkRows / 16), k = I % (kChunkRows / 16);
     constexpr uint32_t half = h * kHalfLanes;
     constexpr uint32_t offset = h * kBlockBytes + k * 2048;
     mma_ss_c<!(kFirst && k == 0)>(o_tmem + half, p_desc + ((k * 32) >> 4), x_desc + (offset >> 4), kIdescPV<kFormat>);
-    issue_pv_steps<kFormat, I + 1, kFirst>(o_tmem, p_desc, x_desc);
+    issue_pv_steps<kFormat, I + 1, kFirst, kEnd>(o_tmem, p_desc, x_desc);
   }
 }
 
@@ -531,12 +535,12 @@ __device__ __forceinline__ void issue_pv_steps(uint32_t o_tmem, uint64_t p_desc,
 // A = P from shared memory (one 128-byte row per head, 32 bytes per K = 16 step); B = X with
 // features contiguous: the four 64-feature blocks of a half are two block positions apart,
 // 8-row groups 1024 bytes apart.
-template <int kFormat>
+template <int kFormat, int kBegin = 0, int kEnd = kPvSteps>
 __device__ __forceinline__ void issue_pv(const Shared& sm, uint32_t tmem, int stage, bool accumulate) {
   const uint64_t x_desc = smem_desc_sw128(sm.base + kSmemKv + stage * kTileBytes, 2 * kBlockBytes, 1024);
   const uint64_t p_desc = smem_desc_sw128(sm.base + kSmemP, 16, 1024);
-  if (accumulate) issue_pv_steps<kFormat, 0, false>(tmem + kTmemO, p_desc, x_desc);
-  else issue_pv_steps<kFormat, 0, true>(tmem + kTmemO, p_desc, x_desc);
+  if (accumulate) issue_pv_steps<kFormat, kBegin, false, kEnd>(tmem + kTmemO, p_desc, x_desc);
+  else issue_pv_steps<kFormat, kBegin, true, kEnd>(tmem + kTmemO, p_desc, x_desc);
 }
 
 template <int kFormat>
@@ -573,8 +577,7 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
     PROF_BEGIN;
     issue_pv<kFormat>(sm, tmem, c % kStages, !pending_first);
     PROF_END(6);
-    mma_commit(sm.bar(kKvFree0 + c % kStages));
-    mma_commit(sm.bar(kODone));
+    mma_commit(sm.bar(kKvFree0 + c % kStages));  // frees the ring stage and tells the softmax warps
     TRACE(sm, 12, c);
     pending = false;
     return true;
@@ -608,13 +611,12 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
         if (!mbar_wait(sm.bar(kQFull), working_tokens & 1, abort_flag)) return;
         PROF_END(1);
       }
+      // One barrier says both that the tile has landed and that the single score buffer is free
+      // (the softmax warps have read chunk c - 1 out of it): a barrier operation costs this thread
+      // a hundred cycles or more while the copies keep the shared memory pipeline busy.
       PROF_BEGIN;
       if (!mbar_wait(sm.bar(kKvFull0 + stage), (c / kStages) & 1, abort_flag)) return;
       PROF_END(2);
-      PROF_BEGIN;
-      // The single score buffer is free once the softmax warps have read chunk c - 1 out of it.
-      if (c > 0 && !mbar_wait(sm.bar(kSFree), (c - 1) & 1, abort_flag)) return;
-      PROF_END(4);
       tc_fence_after_sync();
       TRACE(sm, 13, c);
       PROF_BEGIN;
@@ -671,10 +673,11 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   __nv_bfloat16* out_base = static_cast<__nv_bfloat16*>(p.out);
   const uint32_t s_addr = tmem + kTmemS + lane_base;
 
+  if (lane == 0) mbar_arrive(sm.bar(kKvFull0));  // the score buffer starts out free (first chunk, stage 0)
   // PVs complete in order: wait until those of chunks 0 .. upto - 1 have.
   auto wait_pv = [&](uint32_t upto) -> bool {
-    while (pv_waited < upto) {
-      if (!warp_wait(sm.bar(kODone), pv_waited & 1, abort_flag)) return false;
+    while (pv_waited < upto) {  // the PV of chunk c commits to the free barrier of its ring stage
+      if (!warp_wait(sm.bar(kKvFree0 + pv_waited % kStages), (pv_waited / kStages) & 1, abort_flag)) return false;
       ++pv_waited;
     }
     return true;
@@ -786,10 +789,11 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
           if (c < 32) first[c + e] = v; else second[c - 32 + e] = v;
         }
       }
-      // The scores are in registers: the next QK may overwrite the buffer.
+      // The scores are in registers: the next QK may overwrite the buffer. Its tile's full barrier
+      // counts this as well as the copies.
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(sm.bar(kSFree));
+      if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + (chunk_count + 1) % kStages));
 
       const unsigned live = half ? live_hi : live_lo;
       float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -877,7 +881,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
 
   if (threadIdx.x == 0) {
     const int P = kProducerWarps, S = kSoftmaxWarps, T = kProducerThreads;
-    const int counts[kBarCount] = {1, 1, S, S, P, 1, 1, 1, 1, 1, S, S, 1, S, T, T, T};
+    const int counts[kBarCount] = {1, 1, S, S, P, 1, 1, 1, 1, 1, S, S, T + S, T + S, T + S};
     for (int i = 0; i < kBarCount; ++i) mbar_init(sm.bar(i), counts[i]);
     mbar_fence_init();
     *sm.abort_flag() = 0;
