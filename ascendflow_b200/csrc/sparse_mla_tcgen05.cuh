@@ -417,6 +417,13 @@ __device__ void producer_role(const Params& p, const Shared& sm, uint32_t tmem) 
     ++q_step;
   };
   TokenWalk walk(p);
+  // The first token's Q does not depend on the resolver: its loads go out while the token is
+  // being resolved (a block that only gets a few tokens spends a good part of its time here).
+  staged_token = walk.peek();
+  if (staged_token >= 0) {
+    q_step = 0;
+    while (q_step < kQSteps) q_advance();
+  }
   for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
     PROF_BEGIN;
     if (!warp_wait(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
