@@ -602,10 +602,12 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
     // there yet, or has no work, it must not be held back: the previous token's epilogue waits
     // for it, and the publication of later tokens waits for that epilogue.
     const uint32_t ready = sm.bar(kTokenReady0 + (token_count & 1)), ready_parity = (token_count >> 1) & 1;
-    if (pending && !mbar_test(ready, ready_parity)) { p_ready = false; if (!pv(chunk_count - 1)) return; }
-    PROF_BEGIN;
-    if (!mbar_wait(ready, ready_parity, abort_flag)) return;
-    PROF_END(0);
+    if (!mbar_test(ready, ready_parity)) {
+      if (pending) { p_ready = false; if (!pv(chunk_count - 1)) return; }
+      PROF_BEGIN;
+      if (!mbar_wait(ready, ready_parity, abort_flag)) return;
+      PROF_END(0);
+    }
     const int chunks = sm.info(token_count & 1)->chunks;
     if (chunks == 0) {
       if (pending) { p_ready = false; if (!pv(chunk_count - 1)) return; }
