@@ -4,32 +4,32 @@
 //
 // One persistent block per SM owns one query token at a time (64 heads x 512 features) and
 // walks the token's live 64-row chunks (window rows first, then the compressed ranks in list
-// order, as the reference does: examples/sparse_attention/attention.py:42-64, 147-207):
+// order, as the reference does: examples/sparse_attention/attention.py:42-64, 147-207). The
+// chunks of all the block's tokens form one stream; the issue order is QK(c + 1), PV(c).
 //
 //   resolver warp    resolves slot -> physical row (sparse_mla_common.cuh) up to two tokens ahead.
 //   producer warps   gather the token's rows with 16-byte cp.async into a three-stage ring of
 //                    128-byte-swizzled shared tiles (a row is fetched once and serves as K and
 //                    V), and move the token's Q from global to tensor memory through registers.
-//   MMA warp         one thread issues S = Q X^T and O += P X. Q and P are read from tensor
-//                    memory, X from the shared tile (K-major for QK, MN-major for PV).
-//   softmax warps    tcgen05.ld S, joint online softmax
-//                    with the per-head sink (examples/sparse_attention/attention.py:398-490: one
-//                    maximum and one denominator over window, compressed rows and sink; P rounded
-//                    to BF16 before PV, denominator from unrounded FP32), P back to tensor
-//                    memory, O rescaled only when the running maximum moved by more than 2^8,
-//                    final normalisation and store.
+//   MMA warp         one thread issues S = Q X^T (Q from tensor memory, X K-major from the tile)
+//                    and O += P X (P from a shared tile, X MN-major from the same tile).
+//   softmax warps    tcgen05.ld S, joint online softmax with the per-head sink
+//                    (examples/sparse_attention/attention.py:398-490: one maximum and one
+//                    denominator over window, compressed rows and sink; P rounded to the storage
+//                    type before PV, denominator from unrounded FP32), P to shared memory, O
+//                    rescaled only when the running maximum moved by more than 2^8, final
+//                    normalisation and store (after the next token's first chunk).
 //
-// Tensor memory (512 columns x 128 lanes). An M=64 operand or accumulator occupies lanes 0-15 of
-// each 32-lane subpartition; a second one can live in lanes 16-31 of the same columns, and a
-// tcgen05.mma whose A operand comes from tensor memory needs A and D in the same half. The
-// kernel therefore runs two half problems side by side, lane half 0 and lane half 1:
-//   columns   0-255  O[:, 0:256] (half 0)                O[:, 256:512] (half 1)
-//   columns 256-383  Q[:, 0:256] as BF16 pairs (half 0)  Q[:, 256:512] (half 1)
-//   columns 384-511  two S buffers of 64 columns: half 0 holds the partial scores over features
-//                    0-255, half 1 those over 256-511; the softmax threads add the two with
-//                    one shuffle per score. P (BF16 pairs, 32 columns) then overwrites the
-//                    start of the same buffer in both halves and feeds the two PV halves.
-// Thread (lane & 15) + 16 * half of softmax warp w owns head 16 w + (lane & 15) of that half.
+// Tensor memory (512 columns x 128 lanes), all of it in use:
+//   columns   0-255  O: features 0-255 in lanes 0-15 of every 32-lane subpartition, features
+//                    256-511 in lanes 16-31 (two M = 64 accumulators side by side).
+//   columns 256-383  Q as 16-bit pairs, same split: lanes 0-15 hold Q[:, 0:256] of 16 heads, lanes
+//                    16-31 hold Q[:, 256:512] of the same heads.
+//   columns 384-511  the score buffer of the stacked QK product (see `issue_qk`): a low-half lane
+//                    finds its partial scores in columns 0-63, a high-half lane in columns 64-127.
+// Thread (lane & 15) + 16 * half of softmax warp w owns head 16 w + (lane & 15) of that half; the
+// two lanes of a head add their partial scores with one shuffle per score and split the 64 rows
+// of the chunk between them.
 //
 // Every wait on an mbarrier is bounded (tcgen05_ptx.cuh): on expiry the block records
 // kStatusWaitExpired, all roles leave their loops, tensor memory is released, the kernel returns.
