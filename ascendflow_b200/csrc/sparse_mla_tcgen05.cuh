@@ -785,36 +785,37 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       // warp, so both ranges are read and each lane keeps its own). The two lanes of a head share
       // the softmax work: the low lane owns tile rows 0-31, the high lane rows 32-63; each sends
       // the partner the partial scores of the rows it does not own.
-      float first[32], second[32];  // this lane's partial scores of tile rows 0-31 and 32-63
-#pragma unroll
-      for (int c = 0; c < 64; c += 16) {
-        uint32_t low[16], high[16];
-        tmem_ld16(s_addr + c, low);
-        tmem_ld16(s_addr + 64 + c, high);
-        tmem_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const float v = __uint_as_float(half ? high[e] : low[e]);
-          if (c < 32) first[c + e] = v; else second[c - 32 + e] = v;
-        }
-      }
-      // The scores are in registers: the next QK may overwrite the buffer. Its tile's full barrier
-      // counts this as well as the copies.
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + (chunk_count + 1) % kStages));
-
+      // For row j of its 32 the low lane keeps column j and sends column 32 + j; the high lane
+      // keeps column 96 + j and sends column 64 + j: one select each, straight from the loads.
       const unsigned live = half ? live_hi : live_lo;
       float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       float mine[32];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float total = (half ? second[j] : first[j]) + __shfl_xor_sync(0xffffffffu, half ? first[j] : second[j], 16);
-        mine[j] = ((live >> j) & 1u) ? total * p.scale_log2 : -INFINITY;
-        partial_max[j & 3] = fmaxf(partial_max[j & 3], mine[j]);
+      for (int c = 0; c < 32; c += 16) {
+        uint32_t low_a[16], low_b[16], high_a[16], high_b[16];
+        tmem_ld16(s_addr + c, low_a);            // rows c .. c + 15, low partial
+        tmem_ld16(s_addr + 32 + c, low_b);       // rows 32 + c .., low partial
+        tmem_ld16(s_addr + 64 + c, high_a);      // rows c .., high partial
+        tmem_ld16(s_addr + 96 + c, high_b);      // rows 32 + c .., high partial
+        tmem_wait_ld();
+        if (c == 16) {  // the scores are in registers: the next QK may overwrite the buffer. Its
+                        // tile's full barrier counts this as well as the copies.
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + (chunk_count + 1) % kStages));
+        }
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float keep = __uint_as_float(half ? high_b[e] : low_a[e]);
+          const float send = __uint_as_float(half ? high_a[e] : low_b[e]);
+          const float total = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+          const int j = c + e;
+          mine[j] = ((live >> j) & 1u) ? total : -INFINITY;  // unscaled: the scale goes into the exponent's FMA
+          partial_max[j & 3] = fmaxf(partial_max[j & 3], mine[j]);
+        }
       }
       float chunk_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3]));
-      chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, 16));
+      chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, 16)) * p.scale_log2;  // scale > 0
       // The running maximum only moves when it is exceeded by more than 8 (a factor 256), so the
       // accumulator is rescaled rarely; probabilities stay below 2^8 and all terms of one head
       // share the same reference, which cancels in the final division.
@@ -840,7 +841,7 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       }
       float partial_sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < 32; ++j) { mine[j] = exp2f(mine[j] - run_max); partial_sum[j & 3] += mine[j]; }
+      for (int j = 0; j < 32; ++j) { mine[j] = exp2f(fmaf(mine[j], p.scale_log2, -run_max)); partial_sum[j & 3] += mine[j]; }
       run_sum = run_sum * alpha + ((partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]));
       PROF_END(1);
       PROF_BEGIN;
