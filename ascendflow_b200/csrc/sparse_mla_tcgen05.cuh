@@ -668,6 +668,12 @@ __device__ __forceinline__ uint32_t pack_pair(float a, float b) {  // two FP32 -
   }
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {  // one instruction on sm_100
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <int kFormat>
 __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -782,14 +788,14 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       tc_fence_after_sync();
       // Lane (head, low half) holds Q_lo . X_lo in columns 0-63, lane (head, high half) holds
       // Q_hi . X_hi in columns 64-127 (the column address of a load is the same for the whole
-      // warp, so both ranges are read and each lane keeps its own). The two lanes of a head share
-      // the softmax work: the low lane owns tile rows 0-31, the high lane rows 32-63; each sends
-      // the partner the partial scores of the rows it does not own.
-      // For row j of its 32 the low lane keeps column j and sends column 32 + j; the high lane
-      // keeps column 96 + j and sends column 64 + j: one select each, straight from the loads.
+      // warp, so both ranges are read). The two lanes of a head share the softmax work: the low
+      // lane owns tile rows 0-31, the high lane rows 32-63; each sends the partner the partial
+      // scores of the rows it does not own. For row j of its 32 the low lane keeps column j and
+      // sends column 32 + j; the high lane keeps column 96 + j and sends column 64 + j: one
+      // select each, straight from the loads.
       const unsigned live = half ? live_hi : live_lo;
-      float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      float mine[32];
+      const bool all_live = (live_lo & live_hi) == 0xffffffffu;  // the usual case: nothing to mask
+      float mine[32];  // unscaled scores: the scale goes into the exponent's FMA
 #pragma unroll
       for (int c = 0; c < 32; c += 16) {
         uint32_t low_a[16], low_b[16], high_a[16], high_b[16];
@@ -808,12 +814,22 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
         for (int e = 0; e < 16; ++e) {
           const float keep = __uint_as_float(half ? high_b[e] : low_a[e]);
           const float send = __uint_as_float(half ? high_a[e] : low_b[e]);
-          const float total = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-          const int j = c + e;
-          mine[j] = ((live >> j) & 1u) ? total : -INFINITY;  // unscaled: the scale goes into the exponent's FMA
-          partial_max[j & 3] = fmaxf(partial_max[j & 3], mine[j]);
+          mine[c + e] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
         }
       }
+      if (!all_live) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) mine[j] = ((live >> j) & 1u) ? mine[j] : -INFINITY;
+      }
+      float partial_max[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) partial_max[j] = max3(mine[j], mine[j + 4], mine[j + 8]);
+#pragma unroll
+      for (int j = 12; j < 32; j += 8)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) partial_max[k] = max3(partial_max[k], mine[j + k], mine[j + 4 + k]);
+      partial_max[0] = max3(partial_max[0], mine[28], mine[29]);
+      partial_max[1] = max3(partial_max[1], mine[30], mine[31]);
       float chunk_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3]));
       chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, 16)) * p.scale_log2;  // scale > 0
       // The running maximum only moves when it is exceeded by more than 8 (a factor 256), so the
