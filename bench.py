@@ -39,7 +39,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # ncu captures summarised under profiles/: prefill Q8K/ctx32K (1090.1 MB for 8192 tokens) and
 # decode B16 x 6 queries at ctx 128K (58.97 MB for 96 tokens). Other sizes of the same regime are
 # scaled by token count, since traffic is Q + O + gathered rows per token.
-MEASURED_TRAFFIC_PER_TOKEN = {"prefill": 1087.08e6 / 8192, "decode": 59.03e6 / 96}
+MEASURED_TRAFFIC_PER_TOKEN = {"prefill": 1087.22e6 / 8192, "decode": 59.10e6 / 96}
 L2_BYTES = 126 * 1024 * 1024
 
 
