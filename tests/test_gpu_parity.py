@@ -274,6 +274,38 @@ def test_blocks_walk_through_empty_and_short_tokens(ops):
     S.assert_close(actual, O.reference_fp32_from_data(data, policy), "empty and short tokens")
 
 
+@pytest.mark.parametrize("seed", range(3))
+def test_randomised_long_walks(ops, seed):
+    """Several hundred tokens, so that every persistent block works through a random sequence of
+    long, short and empty tokens: requests of 40-300 queries whose caches hold anything from
+    nothing beyond a few rows to thousands of rows, random index counts, narrowed windows."""
+    rng = np.random.default_rng(5000 + seed)
+    ratio = int(rng.choice([1, 2]))
+    b = int(rng.integers(3, 8))
+    lens = [int(v) for v in rng.integers(40, 301, b)]
+    max_seq = 4096
+    policy = O.make_policy(b, sum(lens), ratio=ratio, max_seq=max_seq, blocks=int(rng.integers(40, 128)))
+    data = O.validation_inputs(policy, str(rng.choice(["mixed", "padding", "replay"])), lens)
+    # Caches shorter than the query count leave the request's first tokens with nothing to see.
+    lengths = np.array([int(rng.choice([rng.integers(1, n + 1), rng.integers(n, max_seq + 1)])) for n in lens], dtype=np.int32)
+    data["seqused_ori_kv"] = lengths
+    data["seqused_cmp_kv"] = (lengths // ratio).astype(np.int32)
+    data["cmp_residual_kv"] = (lengths % ratio).astype(np.int32)
+    span = max(1, max_seq // ratio)
+    for token in range(policy["T"]):
+        count = int(rng.choice([0, 1, 40, 64, 65, 200, 512]))
+        row = np.full(512, -1, dtype=np.int32)
+        row[:count] = np.sort(rng.integers(0, span, count))
+        data["cmp_sparse_indices"][token, 0] = row
+        data["ori_topk_length"][token, 0] = int(rng.choice([0, 0, 0, 1, 64, 100]))
+    tensors, _ = S.to_device(data, policy)
+    binding = ops.kernel("sparse_mla")(*(tensors[name] for name in S.TENSOR_ORDER))
+    assert binding.status()[0] == 0
+    assert np.array_equal(resolved_on_device(ops, tensors, policy), O.resolve_rows(data, policy))
+    actual = S.output_to_numpy(tensors["attention_out"], "bf16")
+    S.assert_close(actual, O.reference_fp32_from_data(data, policy), f"long walk {seed}")
+
+
 def test_gather_experiment_rows_are_bit_exact():
     """The isolated gather experiment (counterpart of the reference's gather study) checks its rows."""
     from ascendflow_b200 import gather_bench
