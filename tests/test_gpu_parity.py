@@ -274,8 +274,8 @@ def test_blocks_walk_through_empty_and_short_tokens(ops):
     S.assert_close(actual, O.reference_fp32_from_data(data, policy), "empty and short tokens")
 
 
-@pytest.mark.parametrize("seed", range(3))
-def test_randomised_long_walks(ops, seed):
+@pytest.mark.parametrize("seed,dtype", [(0, "bf16"), (1, "bf16"), (2, "bf16"), (1, "f16")])
+def test_randomised_long_walks(ops, seed, dtype):
     """Several hundred tokens, so that every persistent block works through a random sequence of
     long, short and empty tokens: requests of 40-300 queries whose caches hold anything from
     nothing beyond a few rows to thousands of rows, random index counts, narrowed windows."""
@@ -284,7 +284,7 @@ def test_randomised_long_walks(ops, seed):
     b = int(rng.integers(3, 8))
     lens = [int(v) for v in rng.integers(40, 301, b)]
     max_seq = 4096
-    policy = O.make_policy(b, sum(lens), ratio=ratio, max_seq=max_seq, blocks=int(rng.integers(40, 128)))
+    policy = O.make_policy(b, sum(lens), ratio=ratio, max_seq=max_seq, dtype=dtype, blocks=int(rng.integers(40, 128)))
     data = O.validation_inputs(policy, str(rng.choice(["mixed", "padding", "replay"])), lens)
     # Caches shorter than the query count leave the request's first tokens with nothing to see.
     lengths = np.array([int(rng.choice([rng.integers(1, n + 1), rng.integers(n, max_seq + 1)])) for n in lens], dtype=np.int32)
@@ -299,11 +299,11 @@ def test_randomised_long_walks(ops, seed):
         data["cmp_sparse_indices"][token, 0] = row
         data["ori_topk_length"][token, 0] = int(rng.choice([0, 0, 0, 1, 64, 100]))
     tensors, _ = S.to_device(data, policy)
-    binding = ops.kernel("sparse_mla")(*(tensors[name] for name in S.TENSOR_ORDER))
+    binding = ops.kernel("sparse_mla" if dtype == "bf16" else "sparse_mla_f16")(*(tensors[name] for name in S.TENSOR_ORDER))
     assert binding.status()[0] == 0
     assert np.array_equal(resolved_on_device(ops, tensors, policy), O.resolve_rows(data, policy))
-    actual = S.output_to_numpy(tensors["attention_out"], "bf16")
-    S.assert_close(actual, O.reference_fp32_from_data(data, policy), f"long walk {seed}")
+    actual = S.output_to_numpy(tensors["attention_out"], dtype)
+    S.assert_close(actual, O.reference_fp32_from_data(data, policy), f"long walk {seed} {dtype}")
 
 
 def test_gather_experiment_rows_are_bit_exact():
