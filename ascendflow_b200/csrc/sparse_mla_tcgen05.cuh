@@ -744,7 +744,7 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
         const int row = i * 4 + (lane >> 3), unit = lane & 7;  // staging row = owning lane
         const uint4 v = *reinterpret_cast<const uint4*>(staging + row * 128 + ((unit ^ (row & 7)) << 4));
         __nv_bfloat16* dst = token_out + (size_t)(warp * 16 + (row & 15)) * kFeatures + (row >> 4) * 256 + c + unit * 8;
-        *reinterpret_cast<uint4*>(dst) = v;
+        __stcs(reinterpret_cast<uint4*>(dst), v);  // written once, read by nobody here
       }
       __syncwarp();
     }
