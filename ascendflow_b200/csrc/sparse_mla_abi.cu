@@ -17,17 +17,6 @@
 namespace sparse_mla {
 namespace {
 
-__global__ void resolve_rows_kernel(const Params p, int32_t* resolved) {
-  __shared__ int rows[kSlots];
-  __shared__ int scratch;
-  for (int token = blockIdx.x; token < p.tokens; token += gridDim.x) {
-    __syncthreads();
-    resolve_token_rows(p, token, rows, &scratch);
-    for (int slot = threadIdx.x; slot < kSlots; slot += blockDim.x)
-      resolved[(size_t)token * kSlots + slot] = rows[slot];
-  }
-}
-
 // Self-test of the bounded wait every role of the attention kernel uses: one warp waits on a
 // barrier that nobody arrives on; the wait must give up after `limit` clocks, record
 // kStatusWaitExpired and let the kernel return normally.
@@ -105,6 +94,7 @@ bool fill(Params& p, void* q, void* ori_kv, void* cmp_kv, void* indices, void* o
   if (B <= 0 || T <= 0 || PAGES <= 0 || workspace == nullptr) return false;
   if (CMP_PAGE != 64 && CMP_PAGE != 128) return false;
   if (B > INT32_MAX || T > INT32_MAX || PAGES > INT32_MAX) return false;
+  if (ORI_BLOCKS < 0 || CMP_BLOCKS < 0) return false;  // the kernels' page check is unsigned
   if (ORI_BLOCKS > INT32_MAX / kPage || CMP_BLOCKS > INT32_MAX / kPage) return false;
   p.q = q; p.ori_kv = ori_kv; p.cmp_kv = cmp_kv;
   p.indices = static_cast<const int32_t*>(indices);
@@ -140,12 +130,19 @@ int multiprocessors() {
   return cached[device];
 }
 
+// The shared-memory attribute of a kernel is a per-device setting: one flag per device. (The
+// per-device caches of this file are plain words written with the same value by whoever gets
+// there first: concurrent first calls repeat the set-up, nothing else.)
 template <typename Kernel>
-int configure_once(Kernel kernel, int bytes, bool& done) {
-  if (done) return 0;
-  cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+int configure_once(Kernel kernel, int bytes, bool (&done)[64]) {
+  int device = 0;
+  cudaError_t error = cudaGetDevice(&device);
   if (error != cudaSuccess) return int(error);
-  done = true;
+  if (device < 0 || device >= 64) return -1;
+  if (done[device]) return 0;
+  error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (error != cudaSuccess) return int(error);
+  done[device] = true;
   return 0;
 }
 
@@ -158,7 +155,9 @@ int clear_workspace(cudaStream_t stream, void* workspace) {
 // library holds these bytes until the process exits. In host code the name below is only a
 // host-side stand-in for the device array, never a device address: the address a kernel can use
 // comes from cudaGetSymbolAddress, once per device, with that device current.
-constexpr size_t kStaticWorkspaceBytes = 1024;
+constexpr size_t kStaticWorkspaceBytes = SPARSE_MLA_STATIC_WORKSPACE_BYTES;
+static_assert(kStaticWorkspaceBytes >= size_t(kWorkspaceBytes),
+              "the static array must hold the workspace of one attention launch");
 static __device__ __align__(256) unsigned char static_workspace[kStaticWorkspaceBytes];
 
 // Device address of `static_workspace` on the current device; nullptr (and *error set) on failure.
@@ -252,7 +251,7 @@ int launch_sparse_mla_warp_mma(void* stream, void* arg_q, void* arg_ori_kv, void
             B, T, PAGES, ORI_BLOCKS, CMP_BLOCKS, CMP_PAGE))
     return -1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  static bool configured = false;
+  static bool configured[64] = {false};
   if (int status = configure_once(warp_mma::attention_kernel<__nv_bfloat16>, warp_mma::kSmemBytes, configured))
     return status;
   if (int status = clear_workspace(s, npu_workspace)) return status;
@@ -276,8 +275,8 @@ int launch_sparse_mla_resolve_rows(void* stream, void* arg_cmp_sparse_indices,
     return -1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int status = clear_workspace(s, npu_workspace)) return status;
-  const int64_t cap = int64_t(multiprocessors()) * 8;
-  resolve_rows_kernel<<<int(T < cap ? T : cap), 128, 0, s>>>(p, static_cast<int32_t*>(arg_resolved_rows));
+  const int64_t blocks = (T + 3) / 4, cap = int64_t(multiprocessors()) * 8;  // four warps = four tokens per block
+  umma::resolve_rows_kernel<<<int(blocks < cap ? blocks : cap), 128, 0, s>>>(p, static_cast<int32_t*>(arg_resolved_rows));
   return int(cudaGetLastError());
 }
 
@@ -317,7 +316,13 @@ int launch_sparse_mla_wait_expiry_selftest(void* stream, void* npu_workspace, in
 }
 
 int read_status_sparse_mla(void* stream, void* npu_workspace, int32_t* host_words) {
-  if (npu_workspace == nullptr || host_words == nullptr) return -1;
+  if (host_words == nullptr) return -1;
+  if (npu_workspace == nullptr) {  // the static array of the current device (address already cached
+                                   // after the first launch_sparse_mla_static_workspace: no allocation)
+    int error = 0;
+    npu_workspace = static_workspace_address(&error);
+    if (npu_workspace == nullptr) return error;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t error = cudaMemcpyAsync(host_words, static_cast<char*>(npu_workspace) + kWorkspaceStatusOffset,
                                       kStatusWords * sizeof(int32_t), cudaMemcpyDeviceToHost, s);

@@ -12,7 +12,8 @@
 //                    128-byte-swizzled shared tiles (a row is fetched once and serves as K and
 //                    V), and move the token's Q from global to tensor memory through registers.
 //   MMA warp         one thread issues S = Q X^T (Q from tensor memory, X K-major from the tile)
-//                    and O += P X (P from a shared tile, X MN-major from the same tile).
+//                    and O += P X (P from a shared tile, X MN-major from the same tile; issued
+//                    as tcgen05.mma.ws so that M = 64 does not halve the rate).
 //   softmax warps    tcgen05.ld S, joint online softmax with the per-head sink
 //                    (examples/sparse_attention/attention.py:398-490: one maximum and one
 //                    denominator over window, compressed rows and sink; P rounded to the storage
@@ -21,8 +22,9 @@
 //                    normalisation and store (after the next token's first chunk).
 //
 // Tensor memory (512 columns x 128 lanes), all of it in use:
-//   columns   0-255  O: features 0-255 in lanes 0-15 of every 32-lane subpartition, features
-//                    256-511 in lanes 16-31 (two M = 64 accumulators side by side).
+//   columns   0-255  O: two weight-stationary M = 64, N = 256 accumulators (columns 0-127: features
+//                    0-255, columns 128-255: features 256-511). Lane l holds head l % 64 and,
+//                    of each accumulator, features 128 (l / 64) .. + 127.
 //   columns 256-383  Q as 16-bit pairs, same split: lanes 0-15 hold Q[:, 0:256] of 16 heads, lanes
 //                    16-31 hold Q[:, 256:512] of the same heads.
 //   columns 384-511  the score buffer of the stacked QK product (see `issue_qk`): a low-half lane
@@ -72,7 +74,11 @@ constexpr int kSmemRows = kSmemStore + kSoftmaxWarps * 4096;   // int[2][640]
 constexpr int kSmemInfo = kSmemRows + 2 * kSlots * 4;       // TokenInfo[2]
 constexpr int kSmemBars = kSmemInfo + 2 * 64;               // mbarriers
 constexpr int kSmemMisc = kSmemBars + 32 * 8;               // tmem slot, abort flag
-constexpr int kSmemEnd = kSmemMisc + 64;
+// Per-head factors handed between the softmax warps (float[2][64] each, double-buffered): a
+// thread works out the softmax of one head but reads the accumulator of another (see below).
+constexpr int kSmemAlpha = kSmemMisc + 64;
+constexpr int kSmemInverse = kSmemAlpha + 2 * kHeads * 4;
+constexpr int kSmemEnd = kSmemInverse + 2 * kHeads * 4;
 #ifdef SPARSE_MLA_TRACE
 constexpr int kTraceEntries = 540;
 constexpr int kSmemTrace = kSmemEnd;
@@ -85,7 +91,7 @@ constexpr uint32_t kTmemColumns = 512;
 constexpr uint32_t kTmemO = 0;
 constexpr uint32_t kTmemQ = 256;
 constexpr uint32_t kTmemS = 384;                             // one 128-column score buffer
-constexpr uint32_t kHalfLanes = 16u << 16;                   // lane offset of half 1 in a tensor-memory address
+constexpr uint32_t kTmemOHalf = 128;                         // columns of one 256-feature accumulator
 
 struct TokenInfo {
   int token;
@@ -97,13 +103,13 @@ enum Bar {
   kTokenReady0 = 0, kTokenReady1, kTokenDone0, kTokenDone1, kQFull, kQFree,
   kKvFree0, kKvFree1, kKvFree2,
   kSFull, kPFull, kOFree,
-  kKvFull0, kKvFull1, kKvFull2, kBarCount
+  kKvFull0, kKvFull1, kKvFull2, kSoftmaxSync, kBarCount
 };
 static_assert(kBarCount <= 32, "the barrier area holds 32 mbarriers");
 
 // Storage formats of kind::f16 instructions: 0 = IEEE half, 1 = BF16.
 template <int kFormat> constexpr uint32_t kIdescQK = idesc_f16(128, 128, kFormat, 0, 0);
-template <int kFormat> constexpr uint32_t kIdescPV = idesc_f16(64, 256, kFormat, 0, 1);
+template <int kFormat> constexpr uint32_t kIdescPV = idesc_f16(64, 256, kFormat, 0, 1);  // issued as .ws
 
 // Position of 64-feature block b in a tile: blocks b and b + 4 (the same features of the low
 // and the high half of a row) are neighbours, so that a K-major operand of 128 "rows" with
@@ -244,16 +250,85 @@ __device__ __forceinline__ TokenGeometry token_geometry_warp(const Params& p, in
   return g;
 }
 
+// ---- slot -> physical row, one warp per token -------------------------------------------------
+// The selection of the reference's oracle (benchmarks/attention/sparse_reference.py:107-124) and
+// of its device routines (examples/sparse_attention/gather.py:39-60, 87-131): window slot s is
+// position right - visible + s of the raw cache; compressed rank r is kept when r < min(TOPK,
+// C, cutoff), no entry before it is negative and its index is below the cutoff; a kept entry
+// goes through the request's block table. Lane l returns slots 32 i + l in resolved[i] (the
+// physical cache row, or -1). This one routine serves the attention kernel (its resolver warp)
+// and the index-set export (`resolve_rows_kernel`), so that the exported set is the gathered set.
+__device__ __forceinline__ void resolve_token_warp(const Params& p, int token, int lane,
+                                                   int (&resolved)[kSlots / 32]) {
+  // The index list does not depend on the geometry: its loads go out first.
+  const int32_t* list = p.indices + (size_t)token * kTopK;
+  int index[kTopK / 32];
+#pragma unroll
+  for (int i = 0; i < kTopK / 32; ++i) index[i] = __ldg(list + i * 32 + lane);
+  const TokenGeometry g = token_geometry_warp(p, token, lane);
+  int first = kTopK;
+#pragma unroll
+  for (int i = 0; i < kTopK / 32; ++i)
+    if (index[i] < 0 && first == kTopK) first = i * 32 + lane;
+  const int first_negative = __reduce_min_sync(0xffffffffu, first);
+  const int cmp_shift = p.cmp_page == 64 ? 6 : 7;
+  // Three passes so that all block-table loads are in flight together (a branch or vote between
+  // them would serialise twenty dependent round trips to memory): columns, loads, rows.
+  int column[kSlots / 32], within[kSlots / 32];
+#pragma unroll
+  for (int i = 0; i < kWindow / 32; ++i) {
+    const int slot = i * 32 + lane;
+    const int position = g.right - g.visible + slot;
+    const bool live = slot < g.visible;
+    column[i] = live ? position / kPage : -1;
+    within[i] = position % kPage;
+  }
+#pragma unroll
+  for (int i = 0; i < kTopK / 32; ++i) {
+    const int rank = i * 32 + lane;
+    const bool live = rank < g.bound && rank < first_negative && index[i] < g.cutoff;
+    // cmp_page is 64 or 128: shift and mask instead of a run-time division
+    column[kWindow / 32 + i] = live ? index[i] >> cmp_shift : -1;
+    within[kWindow / 32 + i] = index[i] & (p.cmp_page - 1);
+  }
+#pragma unroll
+  for (int i = 0; i < kSlots / 32; ++i) {
+    const int32_t* table = (i < kWindow / 32 ? p.ori_table : p.cmp_table) + (size_t)g.batch * p.pages;
+    resolved[i] = __ldg(table + min(max(column[i], 0), p.pages - 1));  // the page, for now
+  }
+  bool bad = false;
+#pragma unroll
+  for (int i = 0; i < kSlots / 32; ++i) {
+    const bool window = i < kWindow / 32;
+    const int blocks = window ? p.ori_blocks : p.cmp_blocks, page_rows = window ? kPage : p.cmp_page;
+    const bool live = column[i] >= 0;
+    const bool legal = column[i] < p.pages && (unsigned)resolved[i] < (unsigned)blocks;
+    bad |= live && !legal;
+    resolved[i] = live && legal ? resolved[i] * page_rows + within[i] : -1;
+  }
+  if (bad) report(p, kStatusBadPage, token, lane);
+}
+
+// The gathered index set of every token, written out: one warp per token runs the routine the
+// attention kernel's resolver warp runs.
+__global__ void resolve_rows_kernel(const Params p, int32_t* out) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int token = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; token < p.tokens; token += warps) {
+    int resolved[kSlots / 32];
+    resolve_token_warp(p, token, lane, resolved);
+#pragma unroll
+    for (int i = 0; i < kSlots / 32; ++i) out[(size_t)token * kSlots + i * 32 + lane] = resolved[i];
+  }
+}
+
 // ---- resolver warp ----------------------------------------------------------------------------
 // Runs ahead of everybody else: for each token of this block it resolves the 640 slots into row
 // buffer `token_count & 1`, lists the live chunks and publishes both.
 __device__ void resolver_role(const Params& p, const Shared& sm) {
   const int lane = threadIdx.x & 31;
   volatile int* abort_flag = sm.abort_flag();
-  PROF_DECL;
-  const long long prof_start_ = clock64(); (void)prof_start_;
   uint32_t token_count = 0;
-  PROF_BEGIN;
   TokenWalk walk(p);
   for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
     const int buffer = token_count & 1;
@@ -264,60 +339,8 @@ __device__ void resolver_role(const Params& p, const Shared& sm) {
     // a phase parity can only tell two consecutive phases apart.)
     if (token_count >= 2 &&
         !warp_wait(sm.bar(kTokenDone0 + buffer), ((token_count >> 1) & 1) ^ 1, abort_flag)) return;
-    PROF_END(0);  // since the previous token's publication (or role start): waiting for a free buffer
-    PROF_BEGIN;
-    // The index list does not depend on the geometry: its loads go out first.
-    const int32_t* list = p.indices + (size_t)token * kTopK;
-    int index[kTopK / 32];
-#pragma unroll
-    for (int i = 0; i < kTopK / 32; ++i) index[i] = __ldg(list + i * 32 + lane);
-    const TokenGeometry g = token_geometry_warp(p, token, lane);
-    PROF_END(1);
-    PROF_BEGIN;
-    int first = kTopK;
-#pragma unroll
-    for (int i = 0; i < kTopK / 32; ++i)
-      if (index[i] < 0 && first == kTopK) first = i * 32 + lane;
-    const int first_negative = __reduce_min_sync(0xffffffffu, first);
-    PROF_END(2);
-    PROF_BEGIN;
-    const int cmp_shift = p.cmp_page == 64 ? 6 : 7;
-    // Same selection as resolve_window_slot / resolve_compressed_rank, in three passes so that
-    // all block-table loads are in flight together (a branch or vote between them would
-    // serialise twenty dependent round trips to memory): columns, loads, rows.
-    int resolved[kSlots / 32], column[kSlots / 32], within[kSlots / 32];
-#pragma unroll
-    for (int i = 0; i < kWindow / 32; ++i) {
-      const int slot = i * 32 + lane;
-      const int position = g.right - g.visible + slot;
-      const bool live = slot < g.visible;
-      column[i] = live ? position / kPage : -1;
-      within[i] = position % kPage;
-    }
-#pragma unroll
-    for (int i = 0; i < kTopK / 32; ++i) {
-      const int rank = i * 32 + lane;
-      const bool live = rank < g.bound && rank < first_negative && index[i] < g.cutoff;
-      // cmp_page is 64 or 128: shift and mask instead of a run-time division
-      column[kWindow / 32 + i] = live ? index[i] >> cmp_shift : -1;
-      within[kWindow / 32 + i] = index[i] & (p.cmp_page - 1);
-    }
-#pragma unroll
-    for (int i = 0; i < kSlots / 32; ++i) {
-      const int32_t* table = (i < kWindow / 32 ? p.ori_table : p.cmp_table) + (size_t)g.batch * p.pages;
-      resolved[i] = __ldg(table + min(max(column[i], 0), p.pages - 1));  // the page, for now
-    }
-    bool bad = false;
-#pragma unroll
-    for (int i = 0; i < kSlots / 32; ++i) {
-      const bool window = i < kWindow / 32;
-      const int blocks = window ? p.ori_blocks : p.cmp_blocks, page_rows = window ? kPage : p.cmp_page;
-      const bool live = column[i] >= 0;
-      const bool legal = column[i] < p.pages && (unsigned)resolved[i] < (unsigned)blocks;
-      bad |= live && !legal;
-      resolved[i] = live && legal ? resolved[i] * page_rows + within[i] : -1;
-    }
-    if (bad) report(p, kStatusBadPage, token, lane);
+    int resolved[kSlots / 32];
+    resolve_token_warp(p, token, lane, resolved);
     int live_chunks = 0;  // bit c set: chunk c holds a live slot (same in all lanes)
 #pragma unroll
     for (int i = 0; i < kSlots / 32; ++i) {
@@ -333,13 +356,7 @@ __device__ void resolver_role(const Params& p, const Shared& sm) {
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(sm.bar(kTokenReady0 + buffer));
-    PROF_END(3);
-#ifdef SPARSE_MLA_PROFILE
-    if (token_count == 0) prof_[4] = clock64() - prof_start_;
-#endif
-    PROF_BEGIN;
   }
-  if (lane == 0) { PROF_FLUSH(p, 3); }
 }
 
 // 8 x 8 transpose of 16-byte elements across the eight lanes of an octet: on entry lane a holds
@@ -531,14 +548,14 @@ template <int kFormat, int I, bool kFirst, int kEnd = kPvSteps>
 __device__ __forceinline__ void issue_pv_steps(uint32_t o_tmem, uint64_t p_desc, uint64_t x_desc) {
   if constexpr (I < kEnd) {
     constexpr int h = I / (kChunkRows / 16), k = I % (kChunkRows / 16);
-    constexpr uint32_t half = h * kHalfLanes;
     constexpr uint32_t offset = h * kBlockBytes + k * 2048;
-    mma_ss_c<!(kFirst && k == 0)>(o_tmem + half, p_desc + ((k * 32) >> 4), x_desc + (offset >> 4), kIdescPV<kFormat>);
+    mma_ws_ss_c<!(kFirst && k == 0)>(o_tmem + h * kTmemOHalf, p_desc + ((k * 32) >> 4), x_desc + (offset >> 4), kIdescPV<kFormat>);
     issue_pv_steps<kFormat, I + 1, kFirst, kEnd>(o_tmem, p_desc, x_desc);
   }
 }
 
-// O += P X for one 64-row tile: features 0-255 accumulate in lane half 0, 256-511 in lane half 1.
+// O += P X for one 64-row tile as two weight-stationary M = 64, N = 256 products (features 0-255
+// and 256-511): with 64 heads a plain M = 64 instruction would leave half of the pipe idle.
 // A = P from shared memory (one 128-byte row per head, 32 bytes per K = 16 step); B = X with
 // features contiguous: the four 64-feature blocks of a half are two block positions apart,
 // 8-row groups 1024 bytes apart.
@@ -684,7 +701,21 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   PROF_DECL;
   const long long prof_start_ = clock64(); (void)prof_start_;
   const float sink = __ldg(p.sinks + head) * 1.4426950408889634f;  // log2 domain
-  uint32_t chunk_count = 0, token_count = 0, pv_waited = 0;
+  uint32_t chunk_count = 0, token_count = 0, pv_waited = 0, sync_count = 0;
+  // The accumulator's layout is that of the weight-stationary PV (lane = head for lanes 0-63, the
+  // same heads again for lanes 64-127 with the next 128 features), not that of the scores: this
+  // thread reads O of head `o_head`, features o_feature .. + 127 of each 256-feature half.
+  const int o_head = (warp & 1) * 32 + lane, o_feature = (warp >> 1) * 128;
+  float* alpha_exchange = reinterpret_cast<float*>(sm.ptr + kSmemAlpha);
+  float* inverse_exchange = reinterpret_cast<float*>(sm.ptr + kSmemInverse);
+  // All four softmax warps meet (bounded wait); shared-memory writes before it are visible after it.
+  auto sync_softmax = [&]() -> bool {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(sm.bar(kSoftmaxSync));
+    const bool ok = warp_wait(sm.bar(kSoftmaxSync), sync_count & 1, abort_flag);
+    ++sync_count;
+    return ok;
+  };
   __nv_bfloat16* out_base = static_cast<__nv_bfloat16*>(p.out);
   const uint32_t s_addr = tmem + kTmemS + lane_base;
 
@@ -714,7 +745,10 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
     PROF_END(3);
     PROF_BEGIN;
     if (threadIdx.x == 0) TRACE(sm, 23, done_token);
-    const float inverse = 1.f / (done_sum + __shfl_xor_sync(0xffffffffu, done_sum, 16));
+    const float own_inverse = 1.f / (done_sum + __shfl_xor_sync(0xffffffffu, done_sum, 16));
+    if (half == 0) inverse_exchange[(done_count & 1) * kHeads + head] = own_inverse;
+    if (!sync_softmax()) return false;
+    const float inverse = inverse_exchange[(done_count & 1) * kHeads + o_head];
     unsigned char* staging = sm.ptr + kSmemStore + warp * 4096;
     __nv_bfloat16* token_out = out_base + (size_t)done_token * kHeads * kFeatures;
 #pragma unroll 1
@@ -743,7 +777,8 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       for (int i = 0; i < 8; ++i) {
         const int row = i * 4 + (lane >> 3), unit = lane & 7;  // staging row = owning lane
         const uint4 v = *reinterpret_cast<const uint4*>(staging + row * 128 + ((unit ^ (row & 7)) << 4));
-        __nv_bfloat16* dst = token_out + (size_t)(warp * 16 + (row & 15)) * kFeatures + (row >> 4) * 256 + c + unit * 8;
+        // accumulator columns 0-127: features 0-255 (this warp's 128 of them), 128-255: 256-511
+        __nv_bfloat16* dst = token_out + (size_t)((warp & 1) * 32 + row) * kFeatures + (c >> 7) * 256 + o_feature + (c & 127) + unit * 8;
         __stcs(reinterpret_cast<uint4*>(dst), v);  // written once, read by nobody here
       }
       __syncwarp();
@@ -840,20 +875,28 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
         alpha = exp2f(run_max - chunk_max);
         run_max = chunk_max;
       }
-      if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        // O holds earlier chunks: the previous PV must have landed before it is rescaled.
-        if (!wait_pv(chunk_count)) return;
-        tc_fence_after_sync();
+      if (i > 0) {
+        // O holds earlier chunks. The factor of a head is known to the thread that has its scores;
+        // the head's accumulator rows are in other threads' lanes: hand the factors over.
+        float* exchange = alpha_exchange + (chunk_count & 1) * kHeads;
+        if (half == 0) exchange[head] = alpha;
+        if (!sync_softmax()) return;
+        const float o_alpha = exchange[o_head];
+        if (__any_sync(0xffffffffu, o_alpha != 1.f)) {
+          // the previous PV must have landed before O is rescaled
+          if (!wait_pv(chunk_count)) return;
+          tc_fence_after_sync();
 #pragma unroll 1
-        for (int c = 0; c < 256; c += 16) {
-          uint32_t o[16];
-          tmem_ld16(tmem + kTmemO + c + lane_base, o);
-          tmem_wait_ld();
+          for (int c = 0; c < 256; c += 16) {
+            uint32_t o[16];
+            tmem_ld16(tmem + kTmemO + c + lane_base, o);
+            tmem_wait_ld();
 #pragma unroll
-          for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-          tmem_st16(tmem + kTmemO + c + lane_base, o);
+            for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * o_alpha);
+            tmem_st16(tmem + kTmemO + c + lane_base, o);
+          }
+          tmem_wait_st();
         }
-        tmem_wait_st();
       }
       float partial_sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -907,7 +950,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
 
   if (threadIdx.x == 0) {
     const int P = kProducerWarps, S = kSoftmaxWarps, T = kProducerThreads;
-    const int counts[kBarCount] = {1, 1, S, S, P, 1, 1, 1, 1, 1, S, S, T + S, T + S, T + S};
+    const int counts[kBarCount] = {1, 1, S, S, P, 1, 1, 1, 1, 1, S, S, T + S, T + S, T + S, S};
     for (int i = 0; i < kBarCount; ++i) mbar_init(sm.bar(i), counts[i]);
     mbar_fence_init();
     *sm.abort_flag() = 0;

@@ -130,8 +130,10 @@ int launch_sparse_mla_warp_mma(void* stream, void* arg_q, void* arg_ori_kv, void
 /* ---- Gathered index set export -------------------------------------------------------------
  * Writes, for every token and slot 0..639, the physical cache row the attention kernel gathers
  * (a row of ori_kv viewed as [ORI_BLOCKS*128, 512] for slots < 128, a row of cmp_kv viewed as
- * [CMP_BLOCKS*CMP_PAGE, 512] for the rest) or -1 for a masked slot. It runs the same device
- * routine the attention kernels use to resolve rows. The reference checks the same fact by
+ * [CMP_BLOCKS*CMP_PAGE, 512] for the rest) or -1 for a masked slot. One warp per token runs
+ * `resolve_token_warp`, the device routine that the resolver warp of the tcgen05 attention
+ * kernels (launch_sparse_mla, launch_sparse_mla_f16) runs for every token it gathers; the
+ * warp-MMA cross-check kernel keeps its own block-wide routine. The reference checks the same fact by
  * reading back its gather workspace (benchmarks/attention/run_sparse.py:111-130, 253-262);
  * this kernel keeps gathered rows on chip, so the set is exported instead.
  *   resolved_rows [T, 640] int32 write */
@@ -160,7 +162,8 @@ int launch_sparse_mla_resolve_rows(void* stream, void* arg_cmp_sparse_indices,
  *    invalid sizes return -1 as in launch_sparse_mla.
  *  - All calls on a device share the one array. It is cleared on the stream before each launch,
  *    so calls on the same stream are safe back to back; calls that overlap on the GPU
- *    (different streams, different threads) race on it and must not be made. */
+ *    (different streams, different threads) race on it and must not be made.
+ *  - The status block of the last such call is read with read_status_sparse_mla(stream, NULL, ..). */
 #define SPARSE_MLA_STATIC_WORKSPACE_BYTES 1024
 #define SPARSE_MLA_STATIC_WORKSPACE_TOO_SMALL (-2)
 int launch_sparse_mla_static_workspace(void* stream, void* arg_q, void* arg_ori_kv, void* arg_cmp_kv,
@@ -180,7 +183,9 @@ int launch_sparse_mla_static_workspace(void* stream, void* arg_q, void* arg_ori_
 int launch_sparse_mla_wait_expiry_selftest(void* stream, void* npu_workspace, int64_t limit_cycles);
 
 /* Copies the status block of a workspace to `host_words` (host, SPARSE_MLA_STATUS_WORDS int32)
- * after synchronising `stream`. word 0: a SPARSE_MLA_STATUS_* code, word 1: token, word 2: detail. */
+ * after synchronising `stream`. word 0: a SPARSE_MLA_STATUS_* code, word 1: token, word 2: detail.
+ * `npu_workspace` == NULL reads the static array of launch_sparse_mla_static_workspace on the
+ * current device (no allocation: the array's address is looked up once per device). */
 int read_status_sparse_mla(void* stream, void* npu_workspace, int32_t* host_words);
 
 #ifdef __cplusplus

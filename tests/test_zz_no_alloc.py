@@ -29,6 +29,8 @@ def test_static_workspace_entry_matches_the_ordinary_entry_twice_in_a_row():
     launch = library.launch_sparse_mla_static_workspace
     launch.argtypes = [ct.c_void_p] * 14 + [ct.c_int64] * 6
     launch.restype = ct.c_int
+    library.read_status_sparse_mla.argtypes = [ct.c_void_p, ct.c_void_p, ct.POINTER(ct.c_int32)]
+    library.read_status_sparse_mla.restype = ct.c_int
 
     policy = O.make_policy(4, 16, max_seq=4096, blocks=128)
     stream = torch.cuda.current_stream().cuda_stream
@@ -45,6 +47,9 @@ def test_static_workspace_entry_matches_the_ordinary_entry_twice_in_a_row():
         assert status == 0, f"call {call}: status {status}"
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == allocated
+        words = (ct.c_int32 * 8)()
+        assert library.read_status_sparse_mla(ct.c_void_p(stream), None, words) == 0
+        assert words[0] == 0, f"call {call}: status block {list(words)}"
         actual = S.output_to_numpy(tensors["attention_out"], "bf16")
         # Same kernel on the same inputs: identical, and within the suite's bars of the reference.
         assert np.array_equal(actual, S.output_to_numpy(expected, "bf16")), f"call {call}"
