@@ -80,7 +80,7 @@ constexpr int kSmemAlpha = kSmemMisc + 64;
 constexpr int kSmemInverse = kSmemAlpha + 2 * kHeads * 4;
 constexpr int kSmemEnd = kSmemInverse + 2 * kHeads * 4;
 #ifdef SPARSE_MLA_TRACE
-constexpr int kTraceEntries = 540;
+constexpr int kTraceEntries = 390;
 constexpr int kSmemTrace = kSmemEnd;
 constexpr int kSmemBytes = kSmemTrace + 16 + kTraceEntries * 8 + 1024;
 #else
@@ -708,10 +708,14 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   const int o_head = (warp & 1) * 32 + lane, o_feature = (warp >> 1) * 128;
   float* alpha_exchange = reinterpret_cast<float*>(sm.ptr + kSmemAlpha);
   float* inverse_exchange = reinterpret_cast<float*>(sm.ptr + kSmemInverse);
-  // All four softmax warps meet (bounded wait); shared-memory writes before it are visible after it.
-  auto sync_softmax = [&]() -> bool {
+  // The four softmax warps meet in two steps, with independent work in between so that nobody
+  // idles: `sync_arrive` after a warp's shared-memory writes, `sync_wait` (bounded) before it
+  // reads what the other warps wrote before theirs.
+  auto sync_arrive = [&]() {
     __syncwarp();
     if (lane == 0) mbar_arrive(sm.bar(kSoftmaxSync));
+  };
+  auto sync_wait = [&]() -> bool {
     const bool ok = warp_wait(sm.bar(kSoftmaxSync), sync_count & 1, abort_flag);
     ++sync_count;
     return ok;
@@ -733,7 +737,6 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   // been through the softmax, so that the MMA thread has a P to go on with while O is written out.
   int done_token = -1;          // token whose O is complete (or about to be) and not yet stored
   uint32_t done_count = 0;      // its index in this block's walk
-  float done_sum = 0.f;         // this lane's share of its denominator
 
   // O / denominator -> 16-bit -> global for `done_token`: 64 columns per pass, tensor memory ->
   // registers -> a swizzled per-warp staging tile -> global, so that every store instruction
@@ -745,9 +748,7 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
     PROF_END(3);
     PROF_BEGIN;
     if (threadIdx.x == 0) TRACE(sm, 23, done_token);
-    const float own_inverse = 1.f / (done_sum + __shfl_xor_sync(0xffffffffu, done_sum, 16));
-    if (half == 0) inverse_exchange[(done_count & 1) * kHeads + head] = own_inverse;
-    if (!sync_softmax()) return false;
+    if (!sync_wait()) return false;  // the reciprocal denominators, handed over when the token ended
     const float inverse = inverse_exchange[(done_count & 1) * kHeads + o_head];
     unsigned char* staging = sm.ptr + kSmemStore + warp * 4096;
     __nv_bfloat16* token_out = out_base + (size_t)done_token * kHeads * kFeatures;
@@ -878,13 +879,24 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       if (i > 0) {
         // O holds earlier chunks. The factor of a head is known to the thread that has its scores;
         // the head's accumulator rows are in other threads' lanes: hand the factors over.
-        float* exchange = alpha_exchange + (chunk_count & 1) * kHeads;
-        if (half == 0) exchange[head] = alpha;
-        if (!sync_softmax()) return;
-        const float o_alpha = exchange[o_head];
-        if (__any_sync(0xffffffffu, o_alpha != 1.f)) {
-          // the previous PV must have landed before O is rescaled
-          if (!wait_pv(chunk_count)) return;
+        // They are picked up after the exponentials, when everybody's have long been written.
+        if (half == 0) alpha_exchange[(chunk_count & 1) * kHeads + head] = alpha;
+        sync_arrive();
+      }
+      float partial_sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < 32; ++j) { mine[j] = exp2f(fmaf(mine[j], p.scale_log2, -run_max)); partial_sum[j & 3] += mine[j]; }
+      run_sum = run_sum * alpha + ((partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]));
+      PROF_END(1);
+      PROF_BEGIN;
+      // There is one P tile: the previous chunk's PV must have finished reading it. (In step, that
+      // PV ran right behind the QK whose scores this chunk started from.)
+      if (!wait_pv(chunk_count)) return;
+      PROF_END(2);
+      if (i > 0) {
+        if (!sync_wait()) return;
+        const float o_alpha = alpha_exchange[(chunk_count & 1) * kHeads + o_head];
+        if (__any_sync(0xffffffffu, o_alpha != 1.f)) {  // the previous PV has landed (wait above)
           tc_fence_after_sync();
 #pragma unroll 1
           for (int c = 0; c < 256; c += 16) {
@@ -898,16 +910,6 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
           tmem_wait_st();
         }
       }
-      float partial_sum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int j = 0; j < 32; ++j) { mine[j] = exp2f(fmaf(mine[j], p.scale_log2, -run_max)); partial_sum[j & 3] += mine[j]; }
-      run_sum = run_sum * alpha + ((partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]));
-      PROF_END(1);
-      PROF_BEGIN;
-      // There is one P tile: the previous chunk's PV must have finished reading it. (In step, that
-      // PV ran right behind the QK whose scores this chunk started from.)
-      if (!wait_pv(chunk_count)) return;
-      PROF_END(2);
       // P to shared memory, one 128-byte row per head; this lane writes its 32 rows (64 bytes).
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -926,7 +928,10 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
     }
     done_token = token;
     done_count = token_count;
-    done_sum = run_sum;
+    // Hand the reciprocal denominators over now; the epilogue picks them up a chunk later.
+    const float own_inverse = 1.f / (run_sum + __shfl_xor_sync(0xffffffffu, run_sum, 16));
+    if (half == 0) inverse_exchange[(done_count & 1) * kHeads + head] = own_inverse;
+    sync_arrive();
   }
   if (done_token >= 0 && !epilogue()) return;
 #ifdef SPARSE_MLA_PROFILE

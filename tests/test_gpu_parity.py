@@ -313,3 +313,34 @@ def test_gather_experiment_rows_are_bit_exact():
     records = gather_bench.run(requests=8, queries=4, threads=(256,), depths=(2,), repeats=2)
     assert len(records) == 2 and all(r["rows_exact"] for r in records)
     assert {r["address"] for r in records} == {"lookup", "physical"}
+
+
+@pytest.mark.parametrize("kernel_name,dtype", [("sparse_mla", "bf16"), ("sparse_mla_f16", "f16")])
+def test_maximum_that_grows_in_later_chunks(ops, kernel_name, dtype):
+    """Rows planted late in a token's slot list score far above everything before them, twice:
+    the running maximum of one head moves by much more than the lazy-rescale threshold while
+    the accumulator already holds earlier chunks, so the accumulator rows (which other threads
+    hold than those that know the factor) must be rescaled."""
+    import torch
+
+    from ascendflow_b200 import workloads as W
+
+    storage = torch.bfloat16 if dtype == "bf16" else torch.float16
+    tensors, meta, _ = W.device_case(**W.CONFIGS["cpu_reference_q256_ctx4k"], seed=23, dtype=storage, sigma=0.5)
+    policy = O.make_policy(1, 256, max_seq=4096, dtype=dtype)
+    tokens = [40, 97, 160, 255]
+    resolved = O.resolve_rows(meta, policy, tokens)
+    cmp = tensors["cmp_kv"].view(-1, 512)
+    used = set()
+    for local, token in enumerate(tokens):
+        head = (7 * local + 3) % 64
+        for slot, factor in ((128 + 64 * 2 + 5, 1.0), (128 + 64 * 5 + 40, 3.0), (128 + 64 * 7 + 63, 6.0)):
+            row = int(resolved[local, slot])
+            assert row >= 0 and row not in used
+            used.add(row)
+            cmp[row] = (tensors["q"][token, head].float() * factor).to(storage)
+    binding = ops.kernel(kernel_name)(*tensors.values())
+    assert binding.status()[0] == 0
+    actual = S.output_to_numpy(tensors["attention_out"], dtype)
+    everyone = list(range(256))  # the planted rows are visible to other tokens as well
+    S.assert_close(actual, S.sampled_reference(tensors, meta, policy, everyone), f"late maximum {dtype}")
