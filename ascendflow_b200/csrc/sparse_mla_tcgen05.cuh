@@ -103,7 +103,7 @@ enum Bar {
   kTokenReady0 = 0, kTokenReady1, kTokenDone0, kTokenDone1, kQFull, kQFree,
   kKvFree0, kKvFree1, kKvFree2,
   kSFull, kPFull, kOFree,
-  kKvFull0, kKvFull1, kKvFull2, kSoftmaxSync, kBarCount
+  kKvFull0, kKvFull1, kKvFull2, kSoftmaxSync, kInfoRead0, kInfoRead1, kBarCount
 };
 static_assert(kBarCount <= 32, "the barrier area holds 32 mbarriers");
 
@@ -161,6 +161,11 @@ struct TokenWalk {
     }
   }
   __device__ __forceinline__ int peek() const { TokenWalk copy = *this; return copy.next(); }
+  __device__ __forceinline__ int count() const {  // how many tokens next() hands out in all
+    const int per_round = grid * group;  // at most the SM count times eight
+    const int rounds = tokens / per_round, rest = tokens - rounds * per_round - block * group;
+    return rounds * group + (rest < 0 ? 0 : (rest > group ? group : rest));
+  }
 };
 
 // Compile-time diagnostic: with SPARSE_MLA_TRACE defined, block 0 logs (event, value, SM clock)
@@ -337,8 +342,12 @@ __device__ void resolver_role(const Params& p, const Shared& sm) {
     // The buffer is free once the softmax warps have finished the token that used it two tokens
     // ago. (Barriers that one role may pass without the others keeping up exist once per buffer:
     // a phase parity can only tell two consecutive phases apart.)
+    // ... and once the MMA thread and the producer warps have read its chunk count: for a token
+    // with nothing to do the softmax warps finish without waiting for anybody, and a role that
+    // fell two publications behind could not tell them apart by parity.
     if (token_count >= 2 &&
-        !warp_wait(sm.bar(kTokenDone0 + buffer), ((token_count >> 1) & 1) ^ 1, abort_flag)) return;
+        (!warp_wait(sm.bar(kTokenDone0 + buffer), ((token_count >> 1) & 1) ^ 1, abort_flag) ||
+         !warp_wait(sm.bar(kInfoRead0 + buffer), ((token_count >> 1) & 1) ^ 1, abort_flag))) return;
     int resolved[kSlots / 32];
     resolve_token_warp(p, token, lane, resolved);
     int live_chunks = 0;  // bit c set: chunk c holds a live slot (same in all lanes)
@@ -448,6 +457,8 @@ __device__ void producer_role(const Params& p, const Shared& sm, uint32_t tmem) 
     const int* rows = sm.rows(token_count & 1);
     const TokenInfo* info = sm.info(token_count & 1);
     const int chunks = info->chunks;
+    // (for a working token this is said behind the first tile, off the token's critical path)
+    if (chunks == 0 && lane == 0) mbar_arrive(sm.bar(kInfoRead0 + (token_count & 1)));
     for (int item = 0; item < chunks; ++item, ++ring) {
       const uint32_t stage = ring % kStages, use = ring / kStages;
       PROF_BEGIN;
@@ -479,6 +490,7 @@ __device__ void producer_role(const Params& p, const Shared& sm, uint32_t tmem) 
       }
       cp_async_arrive(sm.bar(kKvFull0 + stage));
       PROF_END(2);
+      if (item == 0 && lane == 0) mbar_arrive(sm.bar(kInfoRead0 + (token_count & 1)));
       if (item == 0) {
         // The token's Q, right behind its first tile. Its registers were filled while the
         // previous token's tiles were being issued, unless this is the block's first working
@@ -609,11 +621,7 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
 
   // This thread needs the number of tokens only (the resolver publishes each token's chunk count):
   // the walk's divisions would sit on the critical path between two tokens.
-  uint32_t my_tokens = 0;
-  {
-    TokenWalk walk(p);
-    while (walk.next() >= 0) ++my_tokens;
-  }
+  const uint32_t my_tokens = uint32_t(TokenWalk(p).count());
   for (; token_count < my_tokens; ++token_count) {
     // The pending PV normally goes out behind the next token's first QK. If that token is not
     // there yet, or has no work, it must not be held back: the previous token's epilogue waits
@@ -627,6 +635,7 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
     }
     const int chunks = sm.info(token_count & 1)->chunks;
     if (chunks == 0) {
+      mbar_arrive(sm.bar(kInfoRead0 + (token_count & 1)));
       if (pending) { p_ready = false; if (!pv(chunk_count - 1)) return; }
       continue;
     }
@@ -658,6 +667,7 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
       if (i + 1 == chunks) mma_commit(sm.bar(kQFree));  // the last QK that reads this token's Q
       TRACE(sm, 14, c);
       if (pending && !pv(c - 1)) return;
+      if (i == 0) mbar_arrive(sm.bar(kInfoRead0 + (token_count & 1)));  // chunk count read (see resolver)
       pending = true;
       pending_first = i == 0;
       pending_token = working_tokens;
@@ -955,7 +965,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
 
   if (threadIdx.x == 0) {
     const int P = kProducerWarps, S = kSoftmaxWarps, T = kProducerThreads;
-    const int counts[kBarCount] = {1, 1, S, S, P, 1, 1, 1, 1, 1, S, S, T + S, T + S, T + S, S};
+    const int counts[kBarCount] = {1, 1, S, S, P, 1, 1, 1, 1, 1, S, S, T + S, T + S, T + S, S, P + 1, P + 1};
     for (int i = 0; i < kBarCount; ++i) mbar_init(sm.bar(i), counts[i]);
     mbar_fence_init();
     *sm.abort_flag() = 0;

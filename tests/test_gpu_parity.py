@@ -344,3 +344,31 @@ def test_maximum_that_grows_in_later_chunks(ops, kernel_name, dtype):
     actual = S.output_to_numpy(tensors["attention_out"], dtype)
     everyone = list(range(256))  # the planted rows are visible to other tokens as well
     S.assert_close(actual, S.sampled_reference(tensors, meta, policy, everyone), f"late maximum {dtype}")
+
+
+def test_every_block_starts_with_a_run_of_empty_tokens(ops):
+    """A first request whose cache holds nothing (1200 queries, seqused_ori_kv = 0) in a call large
+    enough for blocks to take eight consecutive tokens per round: every block's first tokens are
+    empty, so the resolver and the softmax warps could race ahead of the roles that only learn a
+    token's chunk count later. Status stays 0, the empty request's rows are zero, the rest matches."""
+    lens = [1200, 4800]
+    policy = O.make_policy(len(lens), sum(lens), ratio=2, max_seq=8192, blocks=160)
+    data = O.validation_inputs(policy, "mixed", lens)
+    lengths = np.array([0, 5000], dtype=np.int32)
+    data["seqused_ori_kv"] = lengths
+    data["seqused_cmp_kv"] = (lengths // 2).astype(np.int32)
+    data["cmp_residual_kv"] = (lengths % 2).astype(np.int32)
+    rng = np.random.default_rng(91)
+    for token in range(policy["T"]):
+        row = np.full(512, -1, dtype=np.int32)
+        count = int(rng.choice([0, 30, 512]))
+        row[:count] = np.sort(rng.integers(0, 2500, count))
+        data["cmp_sparse_indices"][token, 0] = row
+    tensors, _ = S.to_device(data, policy)
+    binding = ops.kernel("sparse_mla")(*(tensors[name] for name in S.TENSOR_ORDER))
+    assert binding.status()[0] == 0
+    actual = S.output_to_numpy(tensors["attention_out"], "bf16")
+    assert not actual[:lens[0]].any()
+    sample = sorted(rng.choice(np.arange(lens[0], policy["T"]), 96, replace=False).tolist())
+    assert np.array_equal(resolved_on_device(ops, tensors, policy)[sample], O.resolve_rows(data, policy, sample))
+    S.assert_close(actual[sample], S.sampled_reference(tensors, data, policy, sample), "after the empty request")
