@@ -63,12 +63,27 @@ def build_library(force=False, verbose=False):
     return LIBRARY
 
 
+def is_current():
+    """True when the built library matches the sources and flags it would be built from now."""
+    return LIBRARY.exists() and STAMP.exists() and STAMP.read_text() == _identity()
+
+
+def identity():
+    """What the result records say about the binary: compiler flags and a hash of the sources."""
+    return {"flags": " ".join(FLAGS), "source_sha256": _identity(), "library": LIBRARY.name,
+            "library_is_current": is_current()}
+
+
 def library_path():
-    """Path of the built library. A missing library is built if nvcc is here; otherwise this
-    fails loudly: there is no other implementation to fall back to."""
-    if not LIBRARY.exists() and nvcc() is not None:
+    """Path of the built library. A missing or stale library (sources or flags changed since it
+    was built) is rebuilt if nvcc is here; otherwise this fails loudly: there is no other
+    implementation to fall back to, and a stale binary must not be measured or shipped."""
+    if not is_current() and nvcc() is not None:
         build_library()
     require(LIBRARY.exists(),
             f"{LIBRARY} is missing: run `python -c 'import __graft_entry__ as g; g.build()'` "
             "(there is no CPU fallback)", kind=ErrorKind.RESOURCE)
+    require(is_current(),
+            f"{LIBRARY} was built from other sources or flags than those present: rebuild it with "
+            "`python -c 'import __graft_entry__ as g; g.build()'`", kind=ErrorKind.RESOURCE)
     return LIBRARY

@@ -139,7 +139,7 @@ class FakeRuntime:
     def __init__(self, stream=0x5000):
         self.torch, self._closed, self.arenas, self.stream_value = FakeTorch, False, [], stream
 
-    def current_device(self): return 0
+    def current_device(self): return getattr(self, "device_index", 0)
 
     def _context(self, device):
         owner = self
@@ -258,3 +258,20 @@ def test_kernel_launch_checks_parameter_count_and_pointer_count(probe):
 def test_wrong_target_or_name_is_refused(probe):
     with pytest.raises(CompileError, match="metadata is missing"):
         TensorKernel(FakeRuntime(), probe, "absent")
+
+
+def test_two_devices_with_the_same_stream_handle_get_separate_arenas(probe):
+    """The legacy default stream is handle 0 on every GPU: a call on a second device with the same
+    sizes must not reuse the binding (and workspace) made for the first."""
+    runtime = FakeRuntime(stream=0)
+    kernel = TensorKernel(runtime, probe, "probe")
+    kernel(*tensors())
+    first = last_call(probe)[3]
+    runtime.device_index = 1
+    x, y = tensors(x_pointer=0x30000, y_pointer=0x40000)
+    x.device = y.device = SimpleNamespace(type="cuda", index=1)
+    kernel(x, y)
+    assert len(runtime.arenas) == 2 and last_call(probe)[3] != first
+    runtime.device_index = 0
+    kernel(*tensors())
+    assert len(runtime.arenas) == 2 and last_call(probe)[3] == first
