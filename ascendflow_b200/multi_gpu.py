@@ -33,13 +33,15 @@ def shard_for_rank(tensors, rank, world, ratio, mode="auto", weights=None):
     return shard_by_token_range(tensors, t0, t1, ratio)
 
 
-def run_sharded(tensors, ratio=2, *, mode="auto", gather=False, compute=None, group=None, weights=None):
+def run_sharded(tensors, ratio=2, *, mode="auto", gather=False, compute=None, group=None, weights=None,
+                flag_device=None):
     """Run this rank's slice; optionally replicate the full output on every rank.
 
     `tensors` maps the thirteen operator names to tensors holding the WHOLE call on every rank
     (read-only inputs may be replicated or be views of a larger buffer; `attention_out` is
     written only in this rank's token range unless `gather` is set). `compute(shard)` defaults to
-    the CUDA operator. Returns the token range this rank computed.
+    the CUDA operator. `flag_device` is where the one-word failure flag lives (default: the output's
+    device; "cpu" for a host-side process group). Returns the token range this rank computed.
     """
     import torch
     import torch.distributed as dist
@@ -62,7 +64,8 @@ def run_sharded(tensors, ratio=2, *, mode="auto", gather=False, compute=None, gr
     except Exception as error:  # reported on every rank below
         failure = error
     out = tensors["attention_out"]
-    flag = torch.tensor([0 if failure is None else 1], dtype=torch.int32, device=out.device)
+    flag = torch.tensor([0 if failure is None else 1], dtype=torch.int32,
+                        device=out.device if flag_device is None else flag_device)
     dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
     if int(flag.item()):
         raise RuntimeError(

@@ -2,19 +2,26 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
-A step is one call of the operator on one batch of seeded synthetic input. The default
-workload is the prefill configuration the reference's headline numbers are quoted on: B=1,
+A step is one call of the operator on one batch of seeded synthetic input. The headline
+workload is the prefill configuration the reference's first published row is quoted on: B=1,
 8192 queries at the end of a 32768-token context, H=64, D=512, TopK=512 of a 2x-compressed
-cache plus a 128-token window, BF16. With N > 1 (one process per GPU under torchrun) every
-rank runs its own replica of the workload with its own seed: no data-path collective, weak
-scaling; `value` is the work of all ranks over the slowest rank's time.
+cache plus a 128-token window, BF16. The same run also times the reference's other three
+published rows (prefill Q32K, decode B64 and B128 at a 128K context) and attaches them under
+`workloads`, each with its own roofline record.
+
+With N > 1 (one process per GPU under torchrun) ONE call is split over the ranks along its
+natural axis with no exchange on the data path: a prefill call by query-token range (ranges of
+equal attended rows, so the triangular full-causal case is balanced), a decode call by request.
+Every rank builds the same seeded call, runs its slice, and `value` is the whole call's work
+over the slowest rank's time: strong scaling.
 
 Timing mirrors the reference's protocol (its README.md:56-58): CUDA events bracket each
 attention launch on the launching stream, an eviction pass writing four times the L2 size
-runs before every timed launch, input preparation is outside the timed region.
+runs before every timed launch, input preparation is outside the timed region, the median of
+the step durations is reported.
 
 `--impl reference` times the reference's CPU numerical reference (the oracle port) on the host
-cores for the same workload, on a bounded sample of query tokens.
+cores: every step is one whole call of the same workload.
 """
 
 from __future__ import annotations
@@ -36,10 +43,18 @@ METRIC = "sparse_mla_effective_tflops_qk_pv_fma2"
 UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of the attention kernel per query token, from the
-# ncu captures summarised under profiles/: prefill Q8K/ctx32K (1090.1 MB for 8192 tokens) and
-# decode B16 x 6 queries at ctx 128K (58.97 MB for 96 tokens). Other sizes of the same regime are
-# scaled by token count, since traffic is Q + O + gathered rows per token.
-MEASURED_TRAFFIC_PER_TOKEN = {"prefill": 1087.22e6 / 8192, "decode": 59.10e6 / 96}
+# ncu captures summarised under profiles/ (prefill Q8K/ctx32K: whole launch of 8192 tokens; decode
+# B16 x 6 queries at ctx 128K: 96 tokens). Other sizes of the same regime are scaled by token
+# count, since traffic is Q + O + gathered rows per token. The figures belong to the kernel
+# sources whose hash is recorded with them: a line measured with other sources says so.
+MEASURED_TRAFFIC = {
+    "prefill": {"bytes_per_token": 1087.22e6 / 8192, "profile": "profiles/attention_kernel_prefill_q8k_ctx32k.md"},
+    "decode": {"bytes_per_token": 59.10e6 / 96, "profile": "profiles/attention_kernel_decode_b16_q6_ctx128k.md"},
+    "source_sha256": "unrecorded",
+}
+EXTRA_WORKLOADS = ("prefill_q32k_ctx32k", "decode_b64_q6_ctx128k", "decode_b128_q6_ctx128k")
+CONFIG_KEYS = {"heads": 64, "features": 512, "topk": 512, "window": 128, "ratio": 2, "values": "N(0,1)",
+               "seed": 4102026}
 L2_BYTES = 126 * 1024 * 1024
 
 
@@ -53,6 +68,8 @@ def parse():
     parser.add_argument("--cpu-sample-seconds", type=float, default=12.0)
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--no-extra-workloads", action="store_true",
+                        help="time the named workload only (the default also times the other published rows)")
     return parser.parse_args()
 
 
@@ -130,118 +147,287 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(clocks)}
 
 
+
+
 def policy_of(config):
     from oracle import sparse_mla_oracle as O
 
     return O.make_policy(config["batches"], config["batches"] * config["queries"], max_seq=config["max_seq"])
 
 
-def cpu_reference_rate(meta_and_rows, policy, budget_seconds, threads):
-    """Time the oracle's FP32 torch-CPU form on as many sampled tokens as fit the budget.
+def token_weights(config):
+    """Rows each query token attends to (window + compressed), in token order."""
+    import numpy as np
 
-    `meta_and_rows(tokens)` returns (q, sinks, rows per token). Returns the record and the
-    seconds per live row, from which a whole-call time is extrapolated.
-    """
+    offsets = np.arange(config["queries"])
+    right = config["context"] - config["queries"] + offsets + 1
+    one = np.minimum(128, right) + np.minimum(512, right // 2)
+    return np.tile(one, config["batches"])
+
+
+class Call:
+    """One rank's slice of a seeded call, bound to the kernel and ready to launch."""
+
+    def __init__(self, config, rank, world, device):
+        from ascendflow_b200 import multi_gpu, ops, workloads as W
+
+        self.config = config
+        self.whole, self.meta, self.work = W.device_case(**config, seed=CONFIG_KEYS["seed"], device=device)
+        weights = token_weights(config)
+        self.mode = "request" if config["batches"] >= world else "tokens"
+        if world == 1:
+            self.tensors, (self.t0, self.t1) = dict(self.whole), (0, self.work["tokens"])
+        else:
+            self.tensors, (self.t0, self.t1) = multi_gpu.shard_for_rank(
+                self.whole, rank, world, 2, mode=self.mode, weights=weights.tolist() if self.mode == "tokens" else None)
+        self.tokens = self.t1 - self.t0
+        self.live_rows = int(weights[self.t0:self.t1].sum())
+        self.flops = 4 * 64 * 512 * self.live_rows
+        order = ("q", "ori_kv", "cmp_kv", "cmp_sparse_indices", "ori_block_table", "cmp_block_table", "cu_seqlens_q",
+                 "seqused_ori_kv", "seqused_cmp_kv", "cmp_residual_kv", "ori_topk_length", "sinks", "attention_out")
+        self.ordered = {name: self.tensors[name] for name in order}
+        self.launch = ops.kernel("sparse_mla").bind(*self.ordered.values()) if self.tokens else None
+
+    def __call__(self):
+        return self.launch() if self.launch is not None else None
+
+
+def time_launches(call, steps, warmup, flush, barrier, sampler=None):
+    """CUDA-event durations (ms) of `steps` launches, L2 evicted before each; returns (durations, binding)."""
+    import torch
+
+    for _ in range(warmup):
+        flush.zero_()
+        call()
+    barrier()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    if sampler is not None:
+        sampler.mark_begin()
+    binding = None
+    for step in range(steps):
+        flush.zero_()
+        starts[step].record()
+        binding = call()
+        ends[step].record()
+    barrier()
+    return [s.elapsed_time(e) for s, e in zip(starts, ends)], binding
+
+
+def hold_load(call, flush, sampler, seconds=1.2):
+    """nvidia-smi samples every 100 ms: when the timed region is shorter than a second, the same
+    launches keep running (untimed) so that the clock record covers the same load."""
+    import torch
+
+    extra = 0
+    while time.time() - sampler.window[0] < seconds:
+        flush.zero_()
+        call()
+        extra += 1
+        if extra % 8 == 0:
+            torch.cuda.synchronize()
+    torch.cuda.synchronize()
+    sampler.mark_end()
+    return extra
+
+
+def roofline_of(config, work, ms, world, source_sha):
+    """The bound that applies to the workload's regime, from the whole call's algorithmic work, the
+    slowest rank's median launch time and the measured peaks (per GPU; N GPUs: N times the peak)."""
+    peak, source = peaks()
+    decode = config["queries"] <= 16
+    regime = "decode" if decode else "prefill"
+    if decode:
+        achieved = work["unique_bytes"] / (ms * 1e-3) / 1e9 / world
+        record = {"bound": "hbm", "achieved": achieved, "peak": peak["hbm_gbs"], "unit": "GB/s"}
+    else:
+        achieved = work["flops"] / (ms * 1e-3) / 1e12 / world
+        record = {"bound": "tensor", "achieved": achieved, "peak": peak["bf16_tflops"], "unit": "TFLOP/s"}
+    record["frac"] = record["achieved"] / record["peak"]
+    traffic = MEASURED_TRAFFIC[regime]
+    record["traffic"] = traffic["bytes_per_token"] * work["tokens"] / world
+    record["traffic_source"] = (f"ncu capture summarised in {traffic['profile']}, scaled by tokens; captured with "
+                                f"kernel sources {MEASURED_TRAFFIC['source_sha256'][:12]}"
+                                + ("" if MEASURED_TRAFFIC["source_sha256"] == source_sha else
+                                   f" (this run: {source_sha[:12]}, so the figure may be stale)"))
+    record["peak_source"] = f"{source} (burst figure: each launch is timed alone between L2 evictions)"
+    record["per_gpu"] = "achieved is per GPU: the whole call's work / GPUs / slowest rank's time"
+    record["kernel"] = "sparse_mla attention kernel, one launch per step per GPU"
+    record["algorithmic"] = {"flops_per_launch": work["flops"], "unique_bytes_per_launch": work["unique_bytes"],
+                             "logical_bytes_per_launch": work["logical_bytes"]}
+    record["logical_gather_gbs"] = work["logical_bytes"] / (ms * 1e-3) / 1e9
+    if peak.get("bf16_tflops_sustained") and not decode:
+        record["frac_of_sustained_peak"] = record["achieved"] / peak["bf16_tflops_sustained"]
+    return record
+
+
+def end_to_end(call, steps, barrier, device):
+    """The public op with HOST buffers: every step copies this rank's queries, indices, tables and
+    lengths in from pinned memory and reads its whole output slice back. Copy-in of step i + 1,
+    the kernel of step i and the copy-out of step i - 1 overlap on three streams, as a serving
+    loop would run them; the paged KV caches are the operator's resident state."""
+    import torch
+
+    from ascendflow_b200 import ops
+
+    tensors = call.ordered
+    moving = ("q", "cmp_sparse_indices", "ori_block_table", "cmp_block_table", "cu_seqlens_q",
+              "seqused_ori_kv", "seqused_cmp_kv", "cmp_residual_kv", "ori_topk_length", "sinks")
+    pinned = {name: tensors[name].cpu().pin_memory() for name in moving}
+    h2d = sum(t.numel() * t.element_size() for t in pinned.values())
+    d2h = tensors["attention_out"].numel() * tensors["attention_out"].element_size()
+    sets = []
+    for _ in range(2):
+        own = dict(tensors)
+        for name in moving + ("attention_out",):
+            own[name] = torch.empty_like(tensors[name])
+        sets.append((own, torch.empty(tensors["attention_out"].shape, dtype=tensors["attention_out"].dtype).pin_memory()))
+    copy_in, compute, copy_out = (torch.cuda.Stream(device=device) for _ in range(3))
+    consumed, drained = [None, None], [None, None]
+
+    def step(index):
+        own, host_out = sets[index % 2]
+        with torch.cuda.stream(copy_in):
+            if consumed[index % 2] is not None:
+                copy_in.wait_event(consumed[index % 2])
+            for name in moving:
+                own[name].copy_(pinned[name], non_blocking=True)
+            arrived = torch.cuda.Event()
+            arrived.record(copy_in)
+        with torch.cuda.stream(compute):
+            compute.wait_event(arrived)
+            if drained[index % 2] is not None:
+                compute.wait_event(drained[index % 2])
+            if call.tokens:
+                ops.sparse_mla(*own.values())
+            consumed[index % 2] = torch.cuda.Event()
+            consumed[index % 2].record(compute)
+        with torch.cuda.stream(copy_out):
+            copy_out.wait_event(consumed[index % 2])
+            host_out.copy_(own["attention_out"], non_blocking=True)
+            drained[index % 2] = torch.cuda.Event()
+            drained[index % 2].record(copy_out)
+
+    for index in range(2):
+        step(index)
+    barrier()
+    wall = time.perf_counter()
+    for index in range(steps):
+        step(index)
+    barrier()
+    return (time.perf_counter() - wall) * 1e3 / steps, int(h2d), int(d2h)
+
+
+def host_call(config, device):
+    """The workload's tensors on the host for the CPU reference: FP32 queries, FP32 cache images,
+    the metadata, and a function giving a token's gathered rows. Same generator and seed as the
+    GPU arm (on a box without a GPU the CPU generator draws the same distributions)."""
+    import numpy as np
+    import torch
+
+    from ascendflow_b200 import workloads as W
+    from oracle import sparse_mla_oracle as O
+
+    tensors, meta, work = W.device_case(**config, seed=CONFIG_KEYS["seed"], device=device)
+    policy = policy_of(config)
+    ori = tensors["ori_kv"].view(-1, 512).float().cpu().numpy()
+    cmp = tensors["cmp_kv"].view(-1, 512).float().cpu().numpy()
+    q = tensors["q"].float().cpu().numpy()
+    sinks = tensors["sinks"].float().cpu().numpy()
+    del tensors
+
+    def rows_for(tokens):
+        resolved = O.resolve_rows(meta, policy, tokens)
+        rows = []
+        for ids in resolved:
+            head, tail = ids[:128], ids[128:]
+            rows.append(np.concatenate([ori[head[head >= 0]], cmp[tail[tail >= 0]]]))
+        return rows
+
+    return q, sinks, rows_for, policy, work
+
+
+def cpu_reference_seconds(q, sinks, rows_for, policy, tokens, threads):
+    """Seconds the oracle's FP32 torch-CPU form takes on `tokens` (rows gathered outside the clock)."""
     import numpy as np
     import torch
     from oracle import sparse_mla_oracle as O
 
     torch.set_num_threads(threads)
-    tokens_total = policy["T"]
-    rng = np.random.default_rng(17)
-    probe = sorted(rng.choice(tokens_total, size=min(32, tokens_total), replace=False).tolist())
-    q, sinks, rows = meta_and_rows(probe)
-    small = dict(policy, T=len(probe))
-    O.reference_fp32(q, sinks, lambda i: rows[i], small, chunk=32)  # warm the BLAS threads
-    start = time.perf_counter()
-    O.reference_fp32(q, sinks, lambda i: rows[i], small, chunk=32)
-    probe_seconds = time.perf_counter() - start
-    per_token = probe_seconds / len(probe)
-    count = int(max(len(probe), min(tokens_total, budget_seconds / max(per_token, 1e-6))))
-    count = min(count, 4096)
-    sample = sorted(rng.choice(tokens_total, size=count, replace=False).tolist())
-    q, sinks, rows = meta_and_rows(sample)
-    small = dict(policy, T=count)
-    start = time.perf_counter()
-    O.reference_fp32(q, sinks, lambda i: rows[i], small, chunk=128)
-    seconds = time.perf_counter() - start
-    live = sum(len(r) for r in rows)
-    flops = 4 * policy["H"] * policy["D"] * live
-    return {
-        "value": flops / seconds / 1e12,
-        "unit": UNIT,
-        "cores": threads,
-        "kind": "port",
-        "sample": (f"{count} of {tokens_total} query tokens drawn uniformly (seed 17), {live} live rows, "
-                   f"{seconds:.2f} s; FP32 torch-CPU bmm/softmax/bmm in chunks of 128 queries "
-                   "(the reference's numerical reference, restated for the CPU)"),
-        "seconds": seconds,
-        "seconds_per_call_extrapolated": None,
-    }, seconds / max(live, 1)
+    total, live = 0.0, 0
+    for first in range(0, len(tokens), 512):  # bounded memory: 512 tokens of rows at a time
+        piece = tokens[first:first + 512]
+        rows = rows_for(piece)
+        live += sum(len(r) for r in rows)
+        small = dict(policy, T=len(piece))
+        start = time.perf_counter()
+        O.reference_fp32(q[np.asarray(piece)], sinks, lambda i: rows[i], small, chunk=128)
+        total += time.perf_counter() - start
+    return total, live
 
 
-def host_rows_provider(config, seed, sigma=1.0):
-    """Rows for sampled tokens without a GPU: metadata from the workload generator; cache rows
-    are gathered by physical row id (modulo the pool size) from a seeded N(0, sigma) pool, which
-    gives a CPU timing the right shapes, gather pattern and value distribution."""
+def cpu_baseline_record(config, device, budget_seconds, threads):
+    """The CPU baseline beside the GPU number: a bounded, seeded sample of the same call's tokens."""
     import numpy as np
-    from ascendflow_b200 import workloads as W
-    from oracle import sparse_mla_oracle as O
 
-    meta, live = W.host_metadata(config["batches"], config["queries"], config["context"], config["max_seq"], 2, seed)
-    policy = policy_of(config)
-
-    pool_rows = 1 << 15
-    rng = np.random.default_rng(seed + 1)
-    pool = O.round_b16(rng.normal(0, sigma, (pool_rows, 512)).astype(np.float32), "bf16")
-    q_pool = O.round_b16(rng.normal(0, sigma, (256, 64, 512)).astype(np.float32), "bf16")
-
-    def provide(tokens):
-        resolved = O.resolve_rows(meta, policy, tokens)
-        q = q_pool[np.asarray(tokens) % len(q_pool)]
-        rows = [pool[ids[ids >= 0] % pool_rows] for ids in resolved]
-        return q, np.linspace(-2, 2, 64, dtype=np.float32), rows
-
-    return provide, policy, live
+    q, sinks, rows_for, policy, work = host_call(config, device)
+    rng = np.random.default_rng(17)
+    total_tokens = policy["T"]
+    probe = sorted(rng.choice(total_tokens, size=min(64, total_tokens), replace=False).tolist())
+    cpu_reference_seconds(q, sinks, rows_for, policy, probe[:16], threads)  # warm the BLAS threads
+    seconds, live = cpu_reference_seconds(q, sinks, rows_for, policy, probe, threads)
+    count = int(min(total_tokens, 4096, max(len(probe), budget_seconds / max(seconds / len(probe), 1e-6))))
+    sample = sorted(rng.choice(total_tokens, size=count, replace=False).tolist())
+    seconds, live = cpu_reference_seconds(q, sinks, rows_for, policy, sample, threads)
+    return {
+        "value": 4 * 64 * 512 * live / seconds / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
+        "sample": (f"{count} of {total_tokens} query tokens drawn uniformly (seed 17), {live} live rows, "
+                   f"{seconds:.2f} s; FP32 torch-CPU bmm/softmax/bmm in chunks of 128 queries (the reference's "
+                   "numerical reference, restated for the CPU)"),
+        "seconds": seconds,
+        "seconds_per_call_extrapolated": seconds / max(live, 1) * work["live_rows"],
+    }
 
 
 def run_reference(args, config):
-    """The reference arm: its CPU numerical reference on this box's host cores."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """The reference arm: the reference's CPU numerical reference (oracle port) on this box's host
+    cores with all threads; each step is one whole call of the workload."""
+    import torch
+
+    if int(os.environ.get("RANK", "0")) != 0:
         return
     threads = os.cpu_count() or 1
-    provide, policy, live = host_rows_provider(config, 4102026)
-    # steps/warmup bound the work: each step is one bounded sample.
-    budget = max(2.0, min(args.cpu_sample_seconds, 120.0 / max(1, args.steps + args.warmup)))
-    records = []
-    for _ in range(max(1, min(args.warmup, 1))):
-        cpu_reference_rate(provide, policy, min(budget, 2.0), threads)
-    for _ in range(max(1, min(args.steps, 3))):
-        record, per_row = cpu_reference_rate(provide, policy, budget, threads)
-        records.append((record, per_row))
-    record, per_row = max(records, key=lambda item: item[0]["value"])
-    seconds_per_call = per_row * live
-    record["seconds_per_call_extrapolated"] = seconds_per_call
-    value = record["value"]
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    q, sinks, rows_for, policy, work = host_call(config, device)
+    everything = list(range(policy["T"]))
+    for _ in range(min(args.warmup, 1)):
+        cpu_reference_seconds(q, sinks, rows_for, policy, everything[:256], threads)
+    durations = []
+    for _ in range(args.steps):
+        seconds, live = cpu_reference_seconds(q, sinks, rows_for, policy, everything, threads)
+        assert live == work["live_rows"]
+        durations.append(seconds)
+    seconds = statistics.median(durations)
+    value = work["flops"] / seconds / 1e12
+    sample = (f"the whole call ({policy['T']} query tokens, {work['live_rows']} live rows) per step, median of "
+              f"{args.steps} steps; FP32 torch-CPU bmm/softmax/bmm in chunks of 128 queries; gathering the rows "
+              "is outside the clock")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds_per_call * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": args.workload, **config,
-                                        "note": "CPU time per call extrapolated from the sampled tokens"},
-        "cpu_baseline": record,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": args.workload, **config, **CONFIG_KEYS},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
 
 
 def run_b200(args, config):
-    import numpy as np
     import torch
     import torch.distributed as dist
 
-    from ascendflow_b200 import ops, workloads as W
+    from ascendflow_b200 import build, workloads as W
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -252,9 +438,7 @@ def run_b200(args, config):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     warmup = max(args.warmup, 3)
-
-    tensors, meta, work = W.device_case(**config, seed=4102026 + rank, device=device)
-    call = ops.kernel("sparse_mla").bind(*tensors.values())
+    identity = build.identity()
     flush = torch.empty(4 * L2_BYTES, dtype=torch.uint8, device=device)
 
     def barrier():
@@ -262,175 +446,81 @@ def run_b200(args, config):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(warmup):
-        flush.zero_()
-        call()
-    barrier()
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    with ClockSampler(local) as clocks:
-        time.sleep(0.3)  # let the sampler come up before the region starts
-        barrier()
-        clocks.mark_begin()
-        for step in range(args.steps):
-            flush.zero_()
-            starts[step].record()
-            binding = call()
-            ends[step].record()
-        barrier()
-        timed_seconds = time.time() - clocks.window[0]
-        # nvidia-smi samples every 100 ms: when the timed region is shorter than a second, the same
-        # launches keep running (untimed) so that the clock record covers the same load.
-        hold_steps = 0
-        while time.time() - clocks.window[0] < 1.2:
-            flush.zero_()
-            call()
-            hold_steps += 1
-            if hold_steps % 8 == 0:
-                torch.cuda.synchronize()
-        torch.cuda.synchronize()
-        clocks.mark_end()
-    durations = [s.elapsed_time(e) for s, e in zip(starts, ends)]
-    status = binding.status()
-    assert status[0] == 0, f"kernel status block reports {status}"
-    mean_ms = sum(durations) / len(durations)
-    slowest = torch.tensor([mean_ms], dtype=torch.float64, device=device)
-    total_flops = torch.tensor([float(work["flops"])], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
-        dist.all_reduce(total_flops, op=dist.ReduceOp.SUM)
-    ms_per_step = float(slowest.item())
-    value = float(total_flops.item()) / (ms_per_step * 1e-3) / 1e12
-
-    # End to end through the public op with host buffers: every step copies the step's inputs
-    # (queries, indices, tables, lengths) from pinned memory and reads the whole output back.
-    # The paged KV caches are the operator's resident state and stay on the device.
-    e2e = None
-    if not args.no_e2e:
-        moving = ("q", "cmp_sparse_indices", "ori_block_table", "cmp_block_table", "cu_seqlens_q",
-                  "seqused_ori_kv", "seqused_cmp_kv", "cmp_residual_kv", "ori_topk_length", "sinks")
-        pinned = {name: tensors[name].cpu().pin_memory() for name in moving}
-        h2d = sum(t.numel() * t.element_size() for t in pinned.values())
-        d2h = tensors["attention_out"].numel() * tensors["attention_out"].element_size()
-        # Two sets of step tensors so that the copy-in of step i + 1, the kernel of step i and the
-        # copy-out of step i - 1 overlap on three streams, as a serving loop would run them.
-        sets = []
-        for _ in range(2):
-            own = dict(tensors)
-            for name in moving + ("attention_out",):
-                own[name] = torch.empty_like(tensors[name])
-            sets.append((own, torch.empty(tensors["attention_out"].shape,
-                                          dtype=tensors["attention_out"].dtype).pin_memory()))
-        copy_in, compute, copy_out = (torch.cuda.Stream(device=device) for _ in range(3))
-        consumed = [None, None]   # kernel of the step that last used the set has finished
-        drained = [None, None]    # its output has reached the host
-
-        def e2e_step(index):
-            own, host_out = sets[index % 2]
-            with torch.cuda.stream(copy_in):
-                if consumed[index % 2] is not None:
-                    copy_in.wait_event(consumed[index % 2])
-                for name in moving:
-                    own[name].copy_(pinned[name], non_blocking=True)
-                arrived = torch.cuda.Event()
-                arrived.record(copy_in)
-            with torch.cuda.stream(compute):
-                compute.wait_event(arrived)
-                if drained[index % 2] is not None:
-                    compute.wait_event(drained[index % 2])
-                ops.sparse_mla(*own.values())
-                consumed[index % 2] = torch.cuda.Event()
-                consumed[index % 2].record(compute)
-            with torch.cuda.stream(copy_out):
-                copy_out.wait_event(consumed[index % 2])
-                host_out.copy_(own["attention_out"], non_blocking=True)
-                drained[index % 2] = torch.cuda.Event()
-                drained[index % 2].record(copy_out)
-
-        steps = max(4, min(args.steps, 12))
-        for index in range(2):
-            e2e_step(index)
-        barrier()
-        wall = time.perf_counter()
-        for index in range(steps):
-            e2e_step(index)
-        barrier()
-        e2e_ms = torch.tensor([(time.perf_counter() - wall) * 1e3 / steps], dtype=torch.float64, device=device)
+    def slowest(value):
+        boxed = torch.tensor([value], dtype=torch.float64, device=device)
         if world > 1:
-            dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
-        e2e = {"value": float(total_flops.item()) / (float(e2e_ms.item()) * 1e-3) / 1e12, "unit": UNIT,
-               "ms_per_step": float(e2e_ms.item()), "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-               "note": "public op (torch custom-op path) with host buffers: every step copies queries, indices, "
-                       "tables and lengths from pinned memory and reads the whole output back; copy-in, kernel "
-                       "and copy-out of neighbouring steps overlap on three streams; KV caches are the "
-                       "operator's resident state; timed by host clock between device synchronisations"}
+            dist.all_reduce(boxed, op=dist.ReduceOp.MAX)
+        return float(boxed.item())
 
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+    def measure(name, workload, with_e2e):
+        """One workload: device-timed launches, clocks under that load, optionally end to end."""
+        call = Call(workload, rank, world, device)
+        with ClockSampler(local) as clocks:
+            time.sleep(0.3)  # let the sampler come up before the region starts
+            durations, binding = time_launches(call, args.steps, warmup, flush, barrier, clocks)
+            timed_seconds = time.time() - clocks.window[0]
+            held = hold_load(call, flush, clocks)
+        if binding is not None:
+            status = binding.status()
+            assert status[0] == 0, f"{name}: kernel status block reports {status}"
+        own_ms = statistics.median(durations) if call.tokens else 0.0
+        ms = slowest(own_ms)
+        work = call.work
+        record = {
+            "ms_per_step": ms, "value": work["flops"] / (ms * 1e-3) / 1e12, "unit": UNIT,
+            "roofline": roofline_of(workload, work, ms, world, identity["source_sha256"]),
+            "clocks": dict(clocks.summary(), region=f"timed region ({timed_seconds:.2f} s) plus {held} identical "
+                                                    "untimed launches so that the 100 ms sampler sees the load"),
+            "config": {"workload": name, **workload, **CONFIG_KEYS,
+                       "shard": {"mode": call.mode if world > 1 else "none", "ranks": world,
+                                 "tokens_on_rank0": call.tokens, "live_rows_on_rank0": call.live_rows},
+                       "l2": "evicted before every timed launch (504 MiB written)",
+                       "timing": "CUDA events around each launch; median of steps; max over ranks",
+                       "ms_per_step_min": min(durations), "ms_per_step_mean": sum(durations) / len(durations)},
+            "gpu_launches": args.steps if call.tokens else 0,
+        }
+        if with_e2e:
+            steps = max(4, min(args.steps, 12))
+            own, h2d, d2h = end_to_end(call, steps, barrier, device)
+            e2e_ms = slowest(own)
+            record["e2e"] = {
+                "value": work["flops"] / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "note": "public op (torch custom-op path) with host buffers: every step copies this rank's slice "
+                        "of queries, indices, tables and lengths from pinned memory and reads its output slice "
+                        "back (bytes are rank 0's); copy-in, kernel and copy-out of neighbouring steps overlap "
+                        "on three streams; KV caches are the operator's resident state; host clock between "
+                        "device synchronisations, max over ranks"}
+        del call
+        torch.cuda.empty_cache()
+        return record
 
-    peak, source = peaks()
-    own_ms = mean_ms
-    decode = config["queries"] <= 16
-    if decode:
-        achieved = work["unique_bytes"] / (own_ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / peak["hbm_gbs"],
-                    "traffic": MEASURED_TRAFFIC_PER_TOKEN["decode"] * work["tokens"],
-                    "traffic_source": "ncu capture of decode_b16_q6_ctx128k scaled by tokens"}
-    else:
-        achieved = work["flops"] / (own_ms * 1e-3) / 1e12
-        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": achieved / peak["bf16_tflops"],
-                    "traffic": MEASURED_TRAFFIC_PER_TOKEN["prefill"] * work["tokens"],
-                    "traffic_source": "ncu capture of prefill_q8k_ctx32k scaled by tokens"}
-    roofline["peak_source"] = f"{source} (burst figure: each launch is timed alone between L2 evictions)"
-    roofline["kernel"] = "sparse_mla attention kernel, one launch per step"
-    roofline["algorithmic"] = {"flops_per_launch": work["flops"], "unique_bytes_per_launch": work["unique_bytes"],
-                               "logical_bytes_per_launch": work["logical_bytes"]}
-    roofline["logical_gather_gbs"] = work["logical_bytes"] / (own_ms * 1e-3) / 1e9
+    headline = measure(args.workload, config, not args.no_e2e)
+    extras = {}
+    if not args.no_extra_workloads:
+        for name in EXTRA_WORKLOADS:
+            if name != args.workload:
+                extras[name] = measure(name, dict(W.CONFIGS[name]), False)
 
-    record = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, **config, "heads": 64, "features": 512, "topk": 512,
-                   "window": 128, "ratio": 2, "values": "N(0,1)", "seed": 4102026,
-                   "replicas": world, "l2": "evicted before every timed launch (504 MiB written)",
-                   "timing": "CUDA events around each launch; mean of steps; max over ranks",
-                   "ms_per_step_min": min(durations), "ms_per_step_median": statistics.median(durations)},
-        "roofline": roofline,
-        "clocks": dict(clocks.summary(), region=f"timed region ({timed_seconds:.2f} s) plus {hold_steps} identical "
-                                                "untimed launches so that the 100 ms sampler sees the load"),
-        "gpu_launches": args.steps,
-    }
-    if e2e is not None:
-        record["e2e"] = e2e
-    if world == 1 and not args.no_cpu_baseline:
-        policy = policy_of(config)
-        def provide(tokens):
-            import numpy as np
-            from oracle import sparse_mla_oracle as O
-
-            resolved = O.resolve_rows(meta, policy, tokens)
-            ori = tensors["ori_kv"].view(-1, 512)
-            cmp = tensors["cmp_kv"].view(-1, 512)
-            rows = []
-            for ids in resolved:
-                head, tail = ids[:128], ids[128:]
-                head, tail = head[head >= 0], tail[tail >= 0]
-                rows.append(np.concatenate([
-                    ori[torch.as_tensor(head, device=device)].float().cpu().numpy(),
-                    cmp[torch.as_tensor(tail, device=device)].float().cpu().numpy()]))
-            q = tensors["q"][torch.as_tensor(np.asarray(tokens), device=device)].float().cpu().numpy()
-            return q, tensors["sinks"].float().cpu().numpy(), rows
-
-        baseline, per_row = cpu_reference_rate(provide, policy, args.cpu_sample_seconds, os.cpu_count() or 1)
-        baseline["seconds_per_call_extrapolated"] = per_row * work["live_rows"]
-        record["cpu_baseline"] = baseline
-    print(json.dumps(record))
+    if rank == 0:
+        record = {
+            "metric": METRIC, "value": headline["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": headline["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": headline["config"], "roofline": headline["roofline"], "clocks": headline["clocks"],
+            "gpu_launches": headline["gpu_launches"] + sum(r["gpu_launches"] for r in extras.values()),
+            "build": identity,
+        }
+        if "e2e" in headline:
+            record["e2e"] = headline["e2e"]
+        if extras:
+            record["workloads"] = {name: {k: v for k, v in r.items() if k != "gpu_launches"} for name, r in extras.items()}
+            record["workloads"][args.workload] = {k: headline[k] for k in ("ms_per_step", "value", "unit", "roofline", "clocks")}
+        if world == 1 and not args.no_cpu_baseline:
+            record["cpu_baseline"] = cpu_baseline_record(config, device, args.cpu_sample_seconds, os.cpu_count() or 1)
+        print(json.dumps(record))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
