@@ -92,6 +92,7 @@ constexpr uint32_t kTmemO = 0;
 constexpr uint32_t kTmemQ = 256;
 constexpr uint32_t kTmemS = 384;                             // one 128-column score buffer
 constexpr uint32_t kTmemOHalf = 128;                         // columns of one 256-feature accumulator
+constexpr uint32_t kHalfLanes = 16u << 16;                   // lane offset of the high-half lanes in a tensor-memory address
 
 struct TokenInfo {
   int token;
@@ -833,34 +834,30 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       if (threadIdx.x == 0) TRACE(sm, 21, chunk_count);
       tc_fence_after_sync();
       // Lane (head, low half) holds Q_lo . X_lo in columns 0-63, lane (head, high half) holds
-      // Q_hi . X_hi in columns 64-127 (the column address of a load is the same for the whole
-      // warp, so both ranges are read). The two lanes of a head share the softmax work: the low
-      // lane owns tile rows 0-31, the high lane rows 32-63; each sends the partner the partial
-      // scores of the rows it does not own. For row j of its 32 the low lane keeps column j and
-      // sends column 32 + j; the high lane keeps column 96 + j and sends column 64 + j: one
-      // select each, straight from the loads.
+      // Q_hi . X_hi in columns 64-127. The two threads of a head share the softmax work: the low
+      // thread owns tile rows 0-31, the high thread rows 32-63. Both partial scores of a row come
+      // straight to the thread that owns it: a load over the 16 low lanes gives threads 0-15
+      // columns j and threads 16-31 columns 32 + j of the low partials; a load over the 16 high
+      // lanes gives them columns 64 + j and 96 + j of the high partials. No exchange between lanes.
       const unsigned live = half ? live_hi : live_lo;
       const bool all_live = (live_lo & live_hi) == 0xffffffffu;  // the usual case: nothing to mask
       float mine[32];  // unscaled scores: the scale goes into the exponent's FMA
-#pragma unroll
-      for (int c = 0; c < 32; c += 16) {
+      {
         uint32_t low_a[16], low_b[16], high_a[16], high_b[16];
-        tmem_ld16(s_addr + c, low_a);            // rows c .. c + 15, low partial
-        tmem_ld16(s_addr + 32 + c, low_b);       // rows 32 + c .., low partial
-        tmem_ld16(s_addr + 64 + c, high_a);      // rows c .., high partial
-        tmem_ld16(s_addr + 96 + c, high_b);      // rows 32 + c .., high partial
+        tmem_ld16_halves<32>(s_addr, low_a);                       // rows 0-15 | 32-47, low partial
+        tmem_ld16_halves<32>(s_addr + 16, low_b);                  // rows 16-31 | 48-63
+        tmem_ld16_halves<32>(s_addr + kHalfLanes + 64, high_a);    // the same rows, high partial
+        tmem_ld16_halves<32>(s_addr + kHalfLanes + 80, high_b);
         tmem_wait_ld();
-        if (c == 16) {  // the scores are in registers: the next QK may overwrite the buffer. Its
-                        // tile's full barrier counts this as well as the copies.
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + (chunk_count + 1) % kStages));
-        }
+        // The scores are in registers: the next QK may overwrite the buffer. Its tile's full
+        // barrier counts this as well as the copies.
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.bar(kKvFull0 + (chunk_count + 1) % kStages));
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float keep = __uint_as_float(half ? high_b[e] : low_a[e]);
-          const float send = __uint_as_float(half ? high_a[e] : low_b[e]);
-          mine[c + e] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+          mine[e] = __uint_as_float(low_a[e]) + __uint_as_float(high_a[e]);
+          mine[16 + e] = __uint_as_float(low_b[e]) + __uint_as_float(high_b[e]);
         }
       }
       if (!all_live) {
