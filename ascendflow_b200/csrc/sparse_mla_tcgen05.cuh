@@ -614,7 +614,8 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
     PROF_BEGIN;
     issue_pv<kFormat>(sm, tmem, c % kStages, !pending_first);
     PROF_END(6);
-    mma_commit(sm.bar(kKvFree0 + c % kStages));  // frees the ring stage and tells the softmax warps
+    mma_commit(sm.bar(kKvFree0 + c % kStages));  // frees the ring stage for the producers
+    mma_commit(sm.bar(kSoftmaxSync));            // and counts towards the softmax warps' step c + 1
     TRACE(sm, 12, c);
     pending = false;
     return true;
@@ -712,35 +713,33 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   PROF_DECL;
   const long long prof_start_ = clock64(); (void)prof_start_;
   const float sink = __ldg(p.sinks + head) * 1.4426950408889634f;  // log2 domain
-  uint32_t chunk_count = 0, token_count = 0, pv_waited = 0, sync_count = 0;
+  uint32_t chunk_count = 0, token_count = 0;
   // The accumulator's layout is that of the weight-stationary PV (lane = head for lanes 0-63, the
   // same heads again for lanes 64-127 with the next 128 features), not that of the scores: this
   // thread reads O of head `o_head`, features o_feature .. + 127 of each 256-feature half.
   const int o_head = (warp & 1) * 32 + lane, o_feature = (warp >> 1) * 128;
   float* alpha_exchange = reinterpret_cast<float*>(sm.ptr + kSmemAlpha);
   float* inverse_exchange = reinterpret_cast<float*>(sm.ptr + kSmemInverse);
-  // The four softmax warps meet in two steps, with independent work in between so that nobody
-  // idles: `sync_arrive` after a warp's shared-memory writes, `sync_wait` (bounded) before it
-  // reads what the other warps wrote before theirs.
-  auto sync_arrive = [&]() {
-    __syncwarp();
-    if (lane == 0) mbar_arrive(sm.bar(kSoftmaxSync));
-  };
-  auto sync_wait = [&]() -> bool {
-    const bool ok = warp_wait(sm.bar(kSoftmaxSync), sync_count & 1, abort_flag);
-    ++sync_count;
-    return ok;
-  };
   __nv_bfloat16* out_base = static_cast<__nv_bfloat16*>(p.out);
   const uint32_t s_addr = tmem + kTmemS + lane_base;
 
   if (lane == 0) mbar_arrive(sm.bar(kKvFull0));  // the score buffer starts out free (first chunk, stage 0)
-  // PVs complete in order: wait until those of chunks 0 .. upto - 1 have.
-  auto wait_pv = [&](uint32_t upto) -> bool {
-    while (pv_waited < upto) {  // the PV of chunk c commits to the free barrier of its ring stage
-      if (!warp_wait(sm.bar(kKvFree0 + pv_waited % kStages), (pv_waited / kStages) & 1, abort_flag)) return false;
-      ++pv_waited;
-    }
+  // Step c (c >= 1) of this block's chunk stream is one phase of one barrier: it completes once
+  // all four softmax warps have published what they hand each other for chunk c (rescale factors,
+  // or the finished token's reciprocal denominators) AND the PV of chunk c - 1 has completed
+  // (the MMA thread commits every PV to it). A warp arrives as early as it can and waits, once,
+  // right before it needs the others' values, O, or the P tile: one wait per chunk for all three.
+  uint32_t steps_arrived = 0, steps_waited = 0;  // steps 1 .. n are done
+  auto step_arrive = [&](uint32_t step) {
+    if (steps_arrived >= step) return;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(sm.bar(kSoftmaxSync));
+    steps_arrived = step;
+  };
+  auto step_wait = [&](uint32_t step) -> bool {
+    if (steps_waited >= step) return true;
+    if (!warp_wait(sm.bar(kSoftmaxSync), (step - 1) & 1, abort_flag)) return false;
+    steps_waited = step;
     return true;
   };
 
@@ -754,12 +753,14 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   // writes four complete 128-byte lines.
   auto epilogue = [&]() -> bool {
     PROF_BEGIN;
-    if (!wait_pv(chunk_count)) return false;  // its last PV
+    // The token's last PV and everybody's reciprocal denominators: step `chunk_count`. After the
+    // next token's first chunk that step has been waited for already.
+    step_arrive(chunk_count);
+    if (!step_wait(chunk_count)) return false;
     tc_fence_after_sync();
     PROF_END(3);
     PROF_BEGIN;
     if (threadIdx.x == 0) TRACE(sm, 23, done_token);
-    if (!sync_wait()) return false;  // the reciprocal denominators, handed over when the token ended
     const float inverse = inverse_exchange[(done_count & 1) * kHeads + o_head];
     unsigned char* staging = sm.ptr + kSmemStore + warp * 4096;
     __nv_bfloat16* token_out = out_base + (size_t)done_token * kHeads * kFeatures;
@@ -888,8 +889,8 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
         // the head's accumulator rows are in other threads' lanes: hand the factors over.
         // They are picked up after the exponentials, when everybody's have long been written.
         if (half == 0) alpha_exchange[(chunk_count & 1) * kHeads + head] = alpha;
-        sync_arrive();
       }
+      if (chunk_count > 0) step_arrive(chunk_count);
       float partial_sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < 32; ++j) { mine[j] = exp2f(fmaf(mine[j], p.scale_log2, -run_max)); partial_sum[j & 3] += mine[j]; }
@@ -898,10 +899,9 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       PROF_BEGIN;
       // There is one P tile: the previous chunk's PV must have finished reading it. (In step, that
       // PV ran right behind the QK whose scores this chunk started from.)
-      if (!wait_pv(chunk_count)) return;
+      if (chunk_count > 0 && !step_wait(chunk_count)) return;
       PROF_END(2);
       if (i > 0) {
-        if (!sync_wait()) return;
         const float o_alpha = alpha_exchange[(chunk_count & 1) * kHeads + o_head];
         if (__any_sync(0xffffffffu, o_alpha != 1.f)) {  // the previous PV has landed (wait above)
           tc_fence_after_sync();
@@ -938,7 +938,6 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
     // Hand the reciprocal denominators over now; the epilogue picks them up a chunk later.
     const float own_inverse = 1.f / (run_sum + __shfl_xor_sync(0xffffffffu, run_sum, 16));
     if (half == 0) inverse_exchange[(done_count & 1) * kHeads + head] = own_inverse;
-    sync_arrive();
   }
   if (done_token >= 0 && !epilogue()) return;
 #ifdef SPARSE_MLA_PROFILE
@@ -962,7 +961,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
 
   if (threadIdx.x == 0) {
     const int P = kProducerWarps, S = kSoftmaxWarps, T = kProducerThreads;
-    const int counts[kBarCount] = {1, 1, S, S, P, 1, 1, 1, 1, 1, S, S, T + S, T + S, T + S, S, P + 1, P + 1};
+    const int counts[kBarCount] = {1, 1, S, S, P, 1, 1, 1, 1, 1, S, S, T + S, T + S, T + S, S + 1, P + 1, P + 1};
     for (int i = 0; i < kBarCount; ++i) mbar_init(sm.bar(i), counts[i]);
     mbar_fence_init();
     *sm.abort_flag() = 0;
