@@ -108,7 +108,6 @@ bool fill(Params& p, void* q, void* ori_kv, void* cmp_kv, void* indices, void* o
   p.sinks = static_cast<const float*>(sinks);
   p.out = out;
   p.status = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + kWorkspaceStatusOffset);
-  p.scheduler = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + kWorkspaceSchedulerOffset);
   p.batches = int32_t(B); p.tokens = int32_t(T); p.pages = int32_t(PAGES);
   p.cmp_page = int32_t(CMP_PAGE); p.ratio = int32_t(kPage / CMP_PAGE);
   p.ori_blocks = int32_t(ORI_BLOCKS); p.cmp_blocks = int32_t(CMP_BLOCKS);
@@ -151,7 +150,7 @@ int clear_workspace(cudaStream_t stream, void* workspace) {
 }
 
 // Scratch of the entry point that allocates nothing: the workspace of one attention launch
-// (status block + scheduler words) as a file-scope device array. Every GPU that loads this
+// (the status block) as a file-scope device array. Every GPU that loads this
 // library holds these bytes until the process exits. In host code the name below is only a
 // host-side stand-in for the device array, never a device address: the address a kernel can use
 // comes from cudaGetSymbolAddress, once per device, with that device current.

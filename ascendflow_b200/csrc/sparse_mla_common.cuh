@@ -27,9 +27,8 @@ constexpr int kStatusOk = 0;
 constexpr int kStatusBadPage = 1;
 constexpr int kStatusWaitExpired = 2;
 
-// Workspace layout (bytes): [0, 512) status block, [512, 1024) scheduler words.
+// Workspace layout (bytes): [0, 512) status block; the rest of the 1024 bytes is reserved.
 constexpr int kWorkspaceStatusOffset = 0;
-constexpr int kWorkspaceSchedulerOffset = 512;
 constexpr int kWorkspaceBytes = 1024;
 
 struct Params {
@@ -47,7 +46,6 @@ struct Params {
   const float* sinks;        // [64]
   void* out;                 // [T, 64, 512] 16-bit
   int32_t* status;           // kStatusWords
-  int32_t* scheduler;        // scheduler words
   int32_t batches;           // B
   int32_t tokens;            // T
   int32_t pages;             // block-table width

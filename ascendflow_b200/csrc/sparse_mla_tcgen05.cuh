@@ -79,13 +79,7 @@ constexpr int kSmemMisc = kSmemBars + 32 * 8;               // tmem slot, abort 
 constexpr int kSmemAlpha = kSmemMisc + 64;
 constexpr int kSmemInverse = kSmemAlpha + 2 * kHeads * 4;
 constexpr int kSmemEnd = kSmemInverse + 2 * kHeads * 4;
-#ifdef SPARSE_MLA_TRACE
-constexpr int kTraceEntries = 390;
-constexpr int kSmemTrace = kSmemEnd;
-constexpr int kSmemBytes = kSmemTrace + 16 + kTraceEntries * 8 + 1024;
-#else
 constexpr int kSmemBytes = kSmemEnd + 1024;  // + slack for the 1024-byte alignment
-#endif
 
 constexpr uint32_t kTmemColumns = 512;
 constexpr uint32_t kTmemO = 0;
@@ -169,44 +163,6 @@ struct TokenWalk {
   }
 };
 
-// Compile-time diagnostic: with SPARSE_MLA_TRACE defined, block 0 logs (event, value, SM clock)
-// in shared memory and copies the log out through `Params::scheduler` when it finishes.
-#ifdef SPARSE_MLA_TRACE
-// Three private logs (producer thread 0, MMA thread, softmax thread 0), each kTraceEntries / 3
-// entries of (event << 24 | value, clock); word 0..2 of the region hold the three counts.
-__device__ __forceinline__ void trace(const Shared& sm, int event, int value) {
-#ifdef SPARSE_MLA_TRACE_ONLY  // bit mask of the events to keep, so that logging does not stretch the timeline
-  if (!((SPARSE_MLA_TRACE_ONLY >> event) & 1)) return;
-#endif
-  if (blockIdx.x != 0) return;
-  const int role = threadIdx.x == 0 ? 2 : (threadIdx.x == kMmaWarp * 32 ? 1 : 0);
-  unsigned* log = reinterpret_cast<unsigned*>(sm.ptr + kSmemTrace);
-  const unsigned slot = role == 0 ? atomicAdd(&log[0], 1u) : log[role]++;  // several producer threads may log
-  constexpr unsigned per_role = kTraceEntries / 3;
-  if (slot < per_role) {
-    log[4 + 2 * (role * per_role + slot)] = (unsigned(event) << 24) | (unsigned(value) & 0xffffffu);
-    log[5 + 2 * (role * per_role + slot)] = unsigned(clock64());
-  }
-}
-#define TRACE(sm, event, value) trace(sm, event, value)
-#else
-#define TRACE(sm, event, value) do {} while (0)
-#endif
-
-// Compile-time diagnostic: with SPARSE_MLA_PROFILE defined, one thread per role of block 0 sums
-// the SM clocks it spends in each named section and writes them to `Params::scheduler`.
-#ifdef SPARSE_MLA_PROFILE
-#define PROF_DECL long long prof_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long prof_t_ = 0; (void)prof_t_
-#define PROF_BEGIN prof_t_ = clock64()
-#define PROF_END(i) prof_[i] += clock64() - prof_t_
-#define PROF_FLUSH(p, role) if (blockIdx.x == 0) { long long* o = reinterpret_cast<long long*>((p).scheduler) + (role) * 8; for (int i_ = 0; i_ < 8; ++i_) o[i_] = prof_[i_]; }
-#else
-#define PROF_DECL do {} while (0)
-#define PROF_BEGIN do {} while (0)
-#define PROF_END(i) do {} while (0)
-#define PROF_FLUSH(p, role) do {} while (0)
-#endif
-
 // A wait whose outcome is uniform across the calling warp (all 32 lanes must call it).
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
@@ -215,9 +171,6 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 // ---- producer warps ---------------------------------------------------------------------------
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool live) {
-#ifdef SPARSE_MLA_EXPERIMENT_NO_COPY  // diagnostic build: measures the pipeline without gather traffic
-  return;
-#endif
   // A masked slot is zero-filled (source size 0) so the tile never holds non-finite leftovers.
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(live ? 16 : 0));
 }
@@ -395,8 +348,6 @@ __device__ void producer_role(const Params& p, const Shared& sm, uint32_t tmem) 
   const int tid = threadIdx.x - kFirstProducerWarp * 32;
   const int lane = tid & 31;
   volatile int* abort_flag = sm.abort_flag();
-  PROF_DECL;
-  const long long prof_start_ = clock64(); (void)prof_start_;
   const char* window_base = static_cast<const char*>(p.ori_kv);
   const char* compressed_base = static_cast<const char*>(p.cmp_kv);
   // Q goes from global memory to tensor memory through registers, never through the ring. A warp
@@ -452,9 +403,7 @@ __device__ void producer_role(const Params& p, const Shared& sm, uint32_t tmem) 
     while (q_step < kQSteps) q_advance();
   }
   for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
-    PROF_BEGIN;
     if (!warp_wait(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
-    PROF_END(0);
     const int* rows = sm.rows(token_count & 1);
     const TokenInfo* info = sm.info(token_count & 1);
     const int chunks = info->chunks;
@@ -462,11 +411,7 @@ __device__ void producer_role(const Params& p, const Shared& sm, uint32_t tmem) 
     if (chunks == 0 && lane == 0) mbar_arrive(sm.bar(kInfoRead0 + (token_count & 1)));
     for (int item = 0; item < chunks; ++item, ++ring) {
       const uint32_t stage = ring % kStages, use = ring / kStages;
-      PROF_BEGIN;
       if (use > 0 && !warp_wait(sm.bar(kKvFree0 + stage), (use - 1) & 1, abort_flag)) return;
-      PROF_END(1);
-      PROF_BEGIN;
-      if (tid == 0) TRACE(sm, 4, item);
       const uint32_t tile = sm.base + kSmemKv + stage * kTileBytes;
       const int chunk = info->chunk[item];
       // Sixteen threads per row and quarter: eight 16-byte units of block q, eight of block q + 4.
@@ -490,21 +435,15 @@ __device__ void producer_role(const Params& p, const Shared& sm, uint32_t tmem) 
         }
       }
       cp_async_arrive(sm.bar(kKvFull0 + stage));
-      PROF_END(2);
       if (item == 0 && lane == 0) mbar_arrive(sm.bar(kInfoRead0 + (token_count & 1)));
       if (item == 0) {
         // The token's Q, right behind its first tile. Its registers were filled while the
         // previous token's tiles were being issued, unless this is the block's first working
         // token or the walk skipped an empty one. The wait (the previous working token's last
         // QK has read the old Q) cannot depend on this thread: all its tiles have been issued.
-        PROF_BEGIN;
         if (staged_token != token) { staged_token = token; q_step = 0; }
         while (q_step < kQSteps) q_advance();
-        PROF_END(4);
-        PROF_BEGIN;
         if (q_loads > 0 && !warp_wait(sm.bar(kQFree), (q_loads - 1) & 1, abort_flag)) return;
-        PROF_END(5);
-        PROF_BEGIN;
         tc_fence_after_sync();
 #pragma unroll
         for (int j = 0; j < 4; ++j)
@@ -516,16 +455,11 @@ __device__ void producer_role(const Params& p, const Shared& sm, uint32_t tmem) 
         ++q_loads;
         staged_token = walk.peek();  // start on the next token's Q
         q_step = staged_token >= 0 ? 0 : kQSteps;
-        PROF_END(6);
       } else if (item >= kQFirstItem && q_step < kQSteps) {
         q_advance();  // one slice of the next token's Q per tile, so that it never comes as a burst
       }
     }
   }
-#ifdef SPARSE_MLA_PROFILE
-  prof_[7] = clock64() - prof_start_;
-#endif
-  if (tid == 0) { PROF_FLUSH(p, 2); }
 }
 
 // ---- MMA warp (one thread) --------------------------------------------------------------------
@@ -583,8 +517,6 @@ __device__ __forceinline__ void issue_pv(const Shared& sm, uint32_t tmem, int st
 template <int kFormat>
 __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
   volatile int* abort_flag = sm.abort_flag();
-  PROF_DECL;
-  const long long prof_start_ = clock64(); (void)prof_start_;
   // The chunks of all working tokens form one stream: chunk c uses ring stage c % kStages and the
   // c-th phase of the score and P barriers. The issue order is QK(c + 1), PV(c) throughout, also
   // across a token boundary: the first QK of a token is issued before the last PV of the
@@ -598,25 +530,16 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
   // PV of the pending chunk c. Returns false on a failed wait.
   auto pv = [&](uint32_t c) -> bool {
     if (pending_first) {  // the previous token's epilogue must have read O
-      PROF_BEGIN;
       if (!mbar_wait(sm.bar(kOFree), (pending_token & 1) ^ 1, abort_flag)) return false;
-      PROF_END(1);
       tc_fence_after_sync();
     }
-    TRACE(sm, 10, c);
     if (!p_ready) {
-      PROF_BEGIN;
       if (!mbar_wait(sm.bar(kPFull), c & 1, abort_flag)) return false;
-      PROF_END(5);
       tc_fence_after_sync();
     }
-    TRACE(sm, 11, c);
-    PROF_BEGIN;
     issue_pv<kFormat>(sm, tmem, c % kStages, !pending_first);
-    PROF_END(6);
     mma_commit(sm.bar(kKvFree0 + c % kStages));  // frees the ring stage for the producers
     mma_commit(sm.bar(kSoftmaxSync));            // and counts towards the softmax warps' step c + 1
-    TRACE(sm, 12, c);
     pending = false;
     return true;
   };
@@ -631,9 +554,7 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
     const uint32_t ready = sm.bar(kTokenReady0 + (token_count & 1)), ready_parity = (token_count >> 1) & 1;
     if (!mbar_test(ready, ready_parity)) {
       if (pending) { p_ready = false; if (!pv(chunk_count - 1)) return; }
-      PROF_BEGIN;
       if (!mbar_wait(ready, ready_parity, abort_flag)) return;
-      PROF_END(0);
     }
     const int chunks = sm.info(token_count & 1)->chunks;
     if (chunks == 0) {
@@ -644,19 +565,13 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
     for (int i = 0; i < chunks; ++i) {
       const uint32_t c = chunk_count, stage = c % kStages;
       if (i == 0) {  // the token's Q is in tensor memory
-        PROF_BEGIN;
         if (!mbar_wait(sm.bar(kQFull), working_tokens & 1, abort_flag)) return;
-        PROF_END(1);
       }
       // One barrier says both that the tile has landed and that the single score buffer is free
       // (the softmax warps have read chunk c - 1 out of it): a barrier operation costs this thread
       // a hundred cycles or more while the copies keep the shared memory pipeline busy.
-      PROF_BEGIN;
       if (!mbar_wait(sm.bar(kKvFull0 + stage), (c / kStages) & 1, abort_flag)) return;
-      PROF_END(2);
       tc_fence_after_sync();
-      TRACE(sm, 13, c);
-      PROF_BEGIN;
       // The pipe's queue covers only ~150 cycles, so nothing slow may sit between the last QK
       // MMA and the first PV MMA: the P barrier is tested (without blocking) a few MMAs early
       // and waited on only if that failed.
@@ -664,10 +579,8 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
       p_ready = pending && mbar_test(sm.bar(kPFull), (c - 1) & 1);
       if (p_ready) tc_fence_after_sync();
       issue_qk<kFormat, 12, 16>(sm, tmem, stage);
-      PROF_END(3);
       mma_commit(sm.bar(kSFull));
       if (i + 1 == chunks) mma_commit(sm.bar(kQFree));  // the last QK that reads this token's Q
-      TRACE(sm, 14, c);
       if (pending && !pv(c - 1)) return;
       if (i == 0) mbar_arrive(sm.bar(kInfoRead0 + (token_count & 1)));  // chunk count read (see resolver)
       pending = true;
@@ -678,10 +591,6 @@ __device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
     ++working_tokens;
   }
   if (pending) { p_ready = false; if (!pv(chunk_count - 1)) return; }
-#ifdef SPARSE_MLA_PROFILE
-  prof_[7] = clock64() - prof_start_;
-#endif
-  PROF_FLUSH(p, 0);
 }
 
 // ---- softmax / correction / epilogue warps ----------------------------------------------------
@@ -710,8 +619,6 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   const int head = warp * 16 + (lane & 15);
   const uint32_t lane_base = uint32_t(warp * 32) << 16;
   volatile int* abort_flag = sm.abort_flag();
-  PROF_DECL;
-  const long long prof_start_ = clock64(); (void)prof_start_;
   const float sink = __ldg(p.sinks + head) * 1.4426950408889634f;  // log2 domain
   uint32_t chunk_count = 0, token_count = 0;
   // The accumulator's layout is that of the weight-stationary PV (lane = head for lanes 0-63, the
@@ -752,15 +659,11 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   // registers -> a swizzled per-warp staging tile -> global, so that every store instruction
   // writes four complete 128-byte lines.
   auto epilogue = [&]() -> bool {
-    PROF_BEGIN;
     // The token's last PV and everybody's reciprocal denominators: step `chunk_count`. After the
     // next token's first chunk that step has been waited for already.
     step_arrive(chunk_count);
     if (!step_wait(chunk_count)) return false;
     tc_fence_after_sync();
-    PROF_END(3);
-    PROF_BEGIN;
-    if (threadIdx.x == 0) TRACE(sm, 23, done_token);
     const float inverse = inverse_exchange[(done_count & 1) * kHeads + o_head];
     unsigned char* staging = sm.ptr + kSmemStore + warp * 4096;
     __nv_bfloat16* token_out = out_base + (size_t)done_token * kHeads * kFeatures;
@@ -796,8 +699,6 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       }
       __syncwarp();
     }
-    PROF_END(4);
-    if (threadIdx.x == 0) TRACE(sm, 24, done_token);
     if (lane == 0) mbar_arrive(sm.bar(kTokenDone0 + (done_count & 1)));
     done_token = -1;
     return true;
@@ -827,12 +728,7 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       const unsigned live_lo = __ballot_sync(0xffffffffu, rows[chunk * kChunkRows + lane] >= 0);
       const unsigned live_hi = __ballot_sync(0xffffffffu, rows[chunk * kChunkRows + 32 + lane] >= 0);
 
-      if (threadIdx.x == 0) TRACE(sm, 20, chunk_count);
-      PROF_BEGIN;
       if (!warp_wait(sm.bar(kSFull), chunk_count & 1, abort_flag)) return;
-      PROF_END(0);
-      PROF_BEGIN;
-      if (threadIdx.x == 0) TRACE(sm, 21, chunk_count);
       tc_fence_after_sync();
       // Lane (head, low half) holds Q_lo . X_lo in columns 0-63, lane (head, high half) holds
       // Q_hi . X_hi in columns 64-127. The two threads of a head share the softmax work: the low
@@ -895,12 +791,9 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) { mine[j] = exp2f(fmaf(mine[j], p.scale_log2, -run_max)); partial_sum[j & 3] += mine[j]; }
       run_sum = run_sum * alpha + ((partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]));
-      PROF_END(1);
-      PROF_BEGIN;
       // There is one P tile: the previous chunk's PV must have finished reading it. (In step, that
       // PV ran right behind the QK whose scores this chunk started from.)
       if (chunk_count > 0 && !step_wait(chunk_count)) return;
-      PROF_END(2);
       if (i > 0) {
         const float o_alpha = alpha_exchange[(chunk_count & 1) * kHeads + o_head];
         if (__any_sync(0xffffffffu, o_alpha != 1.f)) {  // the previous PV has landed (wait above)
@@ -928,7 +821,6 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
       fence_proxy_async();  // the PV reads the tile through the async proxy
       tc_fence_before_sync();
       __syncwarp();
-      if (threadIdx.x == 0) TRACE(sm, 22, chunk_count);
       if (lane == 0) mbar_arrive(sm.bar(kPFull));
       // The previous token's output, now that the MMA thread has this token's first P to go on with.
       if (done_token >= 0 && !epilogue()) return;
@@ -940,10 +832,6 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
     if (half == 0) inverse_exchange[(done_count & 1) * kHeads + head] = own_inverse;
   }
   if (done_token >= 0 && !epilogue()) return;
-#ifdef SPARSE_MLA_PROFILE
-  prof_[7] = clock64() - prof_start_;
-#endif
-  if (threadIdx.x == 0) { PROF_FLUSH(p, 1); }
 }
 
 // ---- kernel and launch ------------------------------------------------------------------------
@@ -965,9 +853,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
     for (int i = 0; i < kBarCount; ++i) mbar_init(sm.bar(i), counts[i]);
     mbar_fence_init();
     *sm.abort_flag() = 0;
-#ifdef SPARSE_MLA_TRACE
-    for (int i = 0; i < 4; ++i) reinterpret_cast<unsigned*>(sm.ptr + kSmemTrace)[i] = 0;
-#endif
   }
   if (warp == kMmaWarp) { tmem_alloc(smem_u32(tmem_slot), kTmemColumns); tmem_relinquish(); }
   tc_fence_before_sync();
@@ -991,13 +876,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
   __syncthreads();
   if (threadIdx.x == 0 && *sm.abort_flag() != 0) report(p, kStatusWaitExpired, blockIdx.x, 0);
   if (warp == kMmaWarp) tmem_dealloc(tmem, kTmemColumns);
-#ifdef SPARSE_MLA_TRACE
-  if (blockIdx.x == 0) {
-    const unsigned* log = reinterpret_cast<const unsigned*>(sm.ptr + kSmemTrace);
-    unsigned* dst = reinterpret_cast<unsigned*>(p.scheduler);
-    for (int i = threadIdx.x; i < 4 + 2 * kTraceEntries; i += blockDim.x) dst[i] = log[i];
-  }
-#endif
 }
 
 template <int kFormat>

@@ -19,7 +19,7 @@
  *    PAGES = MAX_SEQ / 128 is the block-table width; CMP_PAGE = 128 / RATIO is
  *    the row count of a compressed page (64 for C2, 128 for C1).
  *  - `target` in the metadata is "sm_100a" (the reference writes "dav-2201").
- *  - The workspace is small: a status block and scheduler words.
+ *  - The workspace is small: a status block (the rest of its 1024 bytes is reserved).
  *
  * Every function returns 0 on success. `launch_*` only enqueues work on the
  * given CUDA stream and never synchronises; a non-zero value is the CUDA error
