@@ -54,7 +54,8 @@ constexpr int kProducerWarps = 8;
 constexpr int kMmaWarp = kSoftmaxWarps;                     // warp index 4
 constexpr int kResolverWarp = kSoftmaxWarps + 1;            // warp index 5
 constexpr int kFirstProducerWarp = kSoftmaxWarps + 2;
-constexpr int kThreads = 32 * (kSoftmaxWarps + 2 + kProducerWarps);
+constexpr int kPvWarp = kFirstProducerWarp + kProducerWarps;  // warp index 14
+constexpr int kThreads = 32 * (kSoftmaxWarps + 3 + kProducerWarps);
 constexpr int kProducerThreads = 32 * kProducerWarps;
 
 constexpr int kChunkRows = 64;
@@ -514,83 +515,66 @@ __device__ __forceinline__ void issue_pv(const Shared& sm, uint32_t tmem, int st
   else issue_pv_steps<kFormat, kBegin, true, kEnd>(tmem + kTmemO, p_desc, x_desc);
 }
 
+// Two issuing threads in two warps, one per product. Each follows its own data: the QK thread
+// goes on as soon as a tile has landed and the score buffer is free, the PV thread as soon as a P
+// is complete. The tensor pipe executes what arrives in the order it arrives, so the
+// non-MMA instructions of one thread (barrier waits, commits, fences: a hundred cycles and more
+// each, far beyond what the pipe's short queue covers) run while the other thread's product
+// executes. Both walk the same token and chunk sequence as everybody else.
+
+// S = Q X^T: chunk c of the block's chunk stream uses ring stage c % kStages and the c-th phase of
+// the score barrier.
 template <int kFormat>
-__device__ void mma_role(const Params& p, const Shared& sm, uint32_t tmem) {
+__device__ void qk_role(const Params& p, const Shared& sm, uint32_t tmem) {
   volatile int* abort_flag = sm.abort_flag();
-  // The chunks of all working tokens form one stream: chunk c uses ring stage c % kStages and the
-  // c-th phase of the score and P barriers. The issue order is QK(c + 1), PV(c) throughout, also
-  // across a token boundary: the first QK of a token is issued before the last PV of the
-  // previous one, so that the softmax warps always have scores to work on.
-  uint32_t chunk_count = 0, token_count = 0, working_tokens = 0;
-  bool pending = false;        // a chunk whose QK has been issued and whose PV has not
-  bool pending_first = false;  // it is the first chunk of its token (PV overwrites O)
-  uint32_t pending_token = 0;  // index of its token among the working tokens
-  bool p_ready = false;        // its P has been seen to be complete
-
-  // PV of the pending chunk c. Returns false on a failed wait.
-  auto pv = [&](uint32_t c) -> bool {
-    if (pending_first) {  // the previous token's epilogue must have read O
-      if (!mbar_wait(sm.bar(kOFree), (pending_token & 1) ^ 1, abort_flag)) return false;
-      tc_fence_after_sync();
-    }
-    if (!p_ready) {
-      if (!mbar_wait(sm.bar(kPFull), c & 1, abort_flag)) return false;
-      tc_fence_after_sync();
-    }
-    issue_pv<kFormat>(sm, tmem, c % kStages, !pending_first);
-    mma_commit(sm.bar(kKvFree0 + c % kStages));  // frees the ring stage for the producers
-    mma_commit(sm.bar(kSoftmaxSync));            // and counts towards the softmax warps' step c + 1
-    pending = false;
-    return true;
-  };
-
-  // This thread needs the number of tokens only (the resolver publishes each token's chunk count):
-  // the walk's divisions would sit on the critical path between two tokens.
-  const uint32_t my_tokens = uint32_t(TokenWalk(p).count());
-  for (; token_count < my_tokens; ++token_count) {
-    // The pending PV normally goes out behind the next token's first QK. If that token is not
-    // there yet, or has no work, it must not be held back: the previous token's epilogue waits
-    // for it, and the publication of later tokens waits for that epilogue.
-    const uint32_t ready = sm.bar(kTokenReady0 + (token_count & 1)), ready_parity = (token_count >> 1) & 1;
-    if (!mbar_test(ready, ready_parity)) {
-      if (pending) { p_ready = false; if (!pv(chunk_count - 1)) return; }
-      if (!mbar_wait(ready, ready_parity, abort_flag)) return;
-    }
+  uint32_t chunk_count = 0, working_tokens = 0;
+  const uint32_t my_tokens = uint32_t(TokenWalk(p).count());  // closed form: no walk on this thread
+  for (uint32_t token_count = 0; token_count < my_tokens; ++token_count) {
+    if (!mbar_wait(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
     const int chunks = sm.info(token_count & 1)->chunks;
     if (chunks == 0) {
       mbar_arrive(sm.bar(kInfoRead0 + (token_count & 1)));
-      if (pending) { p_ready = false; if (!pv(chunk_count - 1)) return; }
       continue;
     }
-    for (int i = 0; i < chunks; ++i) {
-      const uint32_t c = chunk_count, stage = c % kStages;
-      if (i == 0) {  // the token's Q is in tensor memory
-        if (!mbar_wait(sm.bar(kQFull), working_tokens & 1, abort_flag)) return;
-      }
+    // the token's Q is in tensor memory
+    if (!mbar_wait(sm.bar(kQFull), working_tokens & 1, abort_flag)) return;
+    for (int i = 0; i < chunks; ++i, ++chunk_count) {
+      const uint32_t stage = chunk_count % kStages;
       // One barrier says both that the tile has landed and that the single score buffer is free
-      // (the softmax warps have read chunk c - 1 out of it): a barrier operation costs this thread
-      // a hundred cycles or more while the copies keep the shared memory pipeline busy.
-      if (!mbar_wait(sm.bar(kKvFull0 + stage), (c / kStages) & 1, abort_flag)) return;
+      // (the softmax warps have read the previous chunk out of it).
+      if (!mbar_wait(sm.bar(kKvFull0 + stage), (chunk_count / kStages) & 1, abort_flag)) return;
       tc_fence_after_sync();
-      // The pipe's queue covers only ~150 cycles, so nothing slow may sit between the last QK
-      // MMA and the first PV MMA: the P barrier is tested (without blocking) a few MMAs early
-      // and waited on only if that failed.
-      issue_qk<kFormat, 0, 12>(sm, tmem, stage);
-      p_ready = pending && mbar_test(sm.bar(kPFull), (c - 1) & 1);
-      if (p_ready) tc_fence_after_sync();
-      issue_qk<kFormat, 12, 16>(sm, tmem, stage);
+      issue_qk<kFormat>(sm, tmem, stage);
       mma_commit(sm.bar(kSFull));
       if (i + 1 == chunks) mma_commit(sm.bar(kQFree));  // the last QK that reads this token's Q
-      if (pending && !pv(c - 1)) return;
       if (i == 0) mbar_arrive(sm.bar(kInfoRead0 + (token_count & 1)));  // chunk count read (see resolver)
-      pending = true;
-      pending_first = i == 0;
-      pending_token = working_tokens;
-      ++chunk_count;
     }
     ++working_tokens;
   }
-  if (pending) { p_ready = false; if (!pv(chunk_count - 1)) return; }
+}
+
+// O += P X (O = P X for a token's first chunk, once the previous token's O has been read out).
+template <int kFormat>
+__device__ void pv_role(const Params& p, const Shared& sm, uint32_t tmem) {
+  volatile int* abort_flag = sm.abort_flag();
+  uint32_t chunk_count = 0, working_tokens = 0;
+  const uint32_t my_tokens = uint32_t(TokenWalk(p).count());
+  for (uint32_t token_count = 0; token_count < my_tokens; ++token_count) {
+    if (!mbar_wait(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
+    const int chunks = sm.info(token_count & 1)->chunks;
+    mbar_arrive(sm.bar(kInfoRead0 + (token_count & 1)));
+    if (chunks == 0) continue;
+    for (int i = 0; i < chunks; ++i, ++chunk_count) {
+      const uint32_t stage = chunk_count % kStages;
+      if (!mbar_wait(sm.bar(kPFull), chunk_count & 1, abort_flag)) return;
+      if (i == 0 && !mbar_wait(sm.bar(kOFree), (working_tokens & 1) ^ 1, abort_flag)) return;
+      tc_fence_after_sync();
+      issue_pv<kFormat>(sm, tmem, stage, i != 0);
+      mma_commit(sm.bar(kKvFree0 + stage));  // frees the ring stage for the producers
+      mma_commit(sm.bar(kSoftmaxSync));      // and counts towards the softmax warps' step c + 1
+    }
+    ++working_tokens;
+  }
 }
 
 // ---- softmax / correction / epilogue warps ----------------------------------------------------
@@ -849,7 +833,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
 
   if (threadIdx.x == 0) {
     const int P = kProducerWarps, S = kSoftmaxWarps, T = kProducerThreads;
-    const int counts[kBarCount] = {1, 1, S, S, P, 1, 1, 1, 1, 1, S, S, T + S, T + S, T + S, S + 1, P + 1, P + 1};
+    const int counts[kBarCount] = {1, 1, S, S, P, 1, 1, 1, 1, 1, S, S, T + S, T + S, T + S, S + 1, P + 2, P + 2};
     for (int i = 0; i < kBarCount; ++i) mbar_init(sm.bar(i), counts[i]);
     mbar_fence_init();
     *sm.abort_flag() = 0;
@@ -863,7 +847,10 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const Params p) 
   if (warp < kSoftmaxWarps) {
     softmax_role<kFormat>(p, sm, tmem);
   } else if (warp == kMmaWarp) {
-    if ((threadIdx.x & 31) == 0) mma_role<kFormat>(p, sm, tmem);
+    if ((threadIdx.x & 31) == 0) qk_role<kFormat>(p, sm, tmem);
+    __syncwarp();
+  } else if (warp == kPvWarp) {
+    if ((threadIdx.x & 31) == 0) pv_role<kFormat>(p, sm, tmem);
     __syncwarp();
   } else if (warp == kResolverWarp) {
     resolver_role(p, sm);
