@@ -148,5 +148,5 @@ def main(root: Path, destination: Path):
 
 
 if __name__ == "__main__":
-    reference_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    reference_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(__file__).resolve().parents[3] / "reference"
     main(reference_root, Path(__file__).with_name("sparse_mla_golden.npz"))
