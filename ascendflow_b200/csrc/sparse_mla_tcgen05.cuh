@@ -73,7 +73,7 @@ constexpr int kSmemP = kSmemKv + kStages * kTileBytes;
 constexpr int kSmemStore = kSmemP + kHeads * 128;
 constexpr int kSmemRows = kSmemStore + kSoftmaxWarps * 4096;   // int[2][640]
 constexpr int kSmemInfo = kSmemRows + 2 * kSlots * 4;       // TokenInfo[2]
-constexpr int kSmemBars = kSmemInfo + 2 * 64;               // mbarriers
+constexpr int kSmemBars = kSmemInfo + 2 * 128;              // mbarriers
 constexpr int kSmemMisc = kSmemBars + 32 * 8;               // tmem slot, abort flag
 // Per-head factors handed between the softmax warps (float[2][64] each, double-buffered): a
 // thread works out the softmax of one head but reads the accumulator of another (see below).
@@ -93,7 +93,9 @@ struct TokenInfo {
   int token;
   int chunks;                 // live chunks of this token
   unsigned char chunk[kMaxChunks];
+  unsigned live[kSlots / 32]; // bit l of word i: slot 32 i + l is live
 };
+static_assert(sizeof(TokenInfo) <= 128, "the info area holds two 128-byte entries");
 
 enum Bar {
   kTokenReady0 = 0, kTokenReady1, kTokenDone0, kTokenDone1, kQFull, kQFree,
@@ -132,7 +134,7 @@ struct Shared {
     return reinterpret_cast<int*>(ptr + kSmemRows) + buffer * kSlots;
   }
   __device__ __forceinline__ TokenInfo* info(int buffer) const {
-    return reinterpret_cast<TokenInfo*>(ptr + kSmemInfo + buffer * 64);
+    return reinterpret_cast<TokenInfo*>(ptr + kSmemInfo + buffer * 128);
   }
   __device__ __forceinline__ volatile int* abort_flag() const {
     return reinterpret_cast<volatile int*>(ptr + kSmemMisc + 4);
@@ -309,7 +311,9 @@ __device__ void resolver_role(const Params& p, const Shared& sm) {
 #pragma unroll
     for (int i = 0; i < kSlots / 32; ++i) {
       rows[i * 32 + lane] = resolved[i];
-      if (__any_sync(0xffffffffu, resolved[i] >= 0)) live_chunks |= 1 << (i * 32 / kChunkRows);
+      const unsigned live = __ballot_sync(0xffffffffu, resolved[i] >= 0);
+      if (live != 0) live_chunks |= 1 << (i * 32 / kChunkRows);
+      if (lane == 0) info->live[i] = live;
     }
     if (lane == 0) {
       int count = 0;
@@ -692,7 +696,6 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
   for (int token = walk.next(); token >= 0; token = walk.next(), ++token_count) {
     if (!warp_wait(sm.bar(kTokenReady0 + (token_count & 1)), (token_count >> 1) & 1, abort_flag)) return;
     const TokenInfo* info = sm.info(token_count & 1);
-    const int* rows = sm.rows(token_count & 1);
     const int chunks = info->chunks;
     if (chunks == 0) {  // nothing visible: the output row is zero whatever the sink
       // The resolver needs the finished token's row buffer back before it can publish the token
@@ -709,8 +712,7 @@ __device__ void softmax_role(const Params& p, const Shared& sm, uint32_t tmem) {
     float run_max = sink, run_sum = half ? 0.f : 1.f;
     for (int i = 0; i < chunks; ++i, ++chunk_count) {
       const int chunk = info->chunk[i];
-      const unsigned live_lo = __ballot_sync(0xffffffffu, rows[chunk * kChunkRows + lane] >= 0);
-      const unsigned live_hi = __ballot_sync(0xffffffffu, rows[chunk * kChunkRows + 32 + lane] >= 0);
+      const unsigned live_lo = info->live[2 * chunk], live_hi = info->live[2 * chunk + 1];
 
       if (!warp_wait(sm.bar(kSFull), chunk_count & 1, abort_flag)) return;
       tc_fence_after_sync();
