@@ -17,7 +17,7 @@ from .diagnostics import ErrorKind, require
 
 PACKAGE = Path(__file__).resolve().parent
 ROOT = PACKAGE.parent
-SOURCES = (PACKAGE / "csrc" / "sparse_mla_abi.cu",)
+SOURCES = (PACKAGE / "csrc" / "sparse_mla_abi.cu", PACKAGE / "csrc" / "sparse_mla_neighbours.cu")
 LIBRARY = PACKAGE / "lib" / "libsparse_mla_sm100a.so"
 STAMP = LIBRARY.with_suffix(".stamp")
 FLAGS = (

@@ -50,7 +50,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 MEASURED_TRAFFIC = {
     "prefill": {"bytes_per_token": 1078.24e6 / 8192, "profile": "profiles/attention_kernel_prefill_q8k_ctx32k.md"},
     "decode": {"bytes_per_token": 59.10e6 / 96, "profile": "profiles/attention_kernel_decode_b16_q6_ctx128k.md"},
-    "source_sha256": "a8de1ec398093eb7ec1d5dca78cad50ee663091b4ce5970887f5fe5c64811092",
+    "source_sha256": "31d15cff6eaacb16b1cec95b37bbd576441bc836a7d5742e7c3d944669904dde",
 }
 EXTRA_WORKLOADS = ("prefill_q32k_ctx32k", "decode_b64_q6_ctx128k", "decode_b128_q6_ctx128k")
 CONFIG_KEYS = {"heads": 64, "features": 512, "topk": 512, "window": 128, "ratio": 2, "values": "N(0,1)",

@@ -175,6 +175,45 @@ int launch_sparse_mla_static_workspace(void* stream, void* arg_q, void* arg_ori_
                                        int64_t PAGES, int64_t ORI_BLOCKS, int64_t CMP_BLOCKS,
                                        int64_t CMP_PAGE);
 
+/* ---- The steps on either side of the operator whose output the operator's inputs fix ----------
+ * No counterpart in the reference: it leaves the indexer, the compressor and the cache writes
+ * to its caller (docs/operators/sparse-mla.md:8, 263-266). These two produce, on the device,
+ * the two inputs of the attention call that change with every step, in the format it reads
+ * (docs/operators/sparse-mla.md:62-87).
+ *
+ * launch_sparse_mla_topk_indices: for every query token, the indices of the TopK = 512 highest
+ * scores among the compressed rows the token may see, i.e. rows [0, min(C, cutoff)) with the
+ * operator's cutoff = max(0, C R + r - n + j + 1) / R; fewer visible rows than 512: all of them.
+ * Ties go to the lower index. Winners are written in ascending order, the rest is -1: exactly
+ * what `cmp_sparse_indices` is. Scores must be finite.
+ *   scores               [T, SPAN]   f32  read  (row stride SPAN, a multiple of 4;
+ *                                                 columns beyond a token's visible rows are ignored)
+ *   cu_seqlens_q         [B + 1]     i32  read
+ *   seqused_cmp_kv       [B]         i32  read
+ *   cmp_residual_kv      [B]         i32  read
+ *   cmp_sparse_indices   [T, 1, 512] i32  write
+ * Returns -1 for sizes out of range (B, T >= 1; SPAN as above; CMP_PAGE 64 or 128, which gives R). */
+int launch_sparse_mla_topk_indices(void* stream, void* arg_scores, void* arg_cu_seqlens_q,
+                                   void* arg_seqused_cmp_kv, void* arg_cmp_residual_kv,
+                                   void* arg_cmp_sparse_indices, int64_t B, int64_t T, int64_t SPAN,
+                                   int64_t CMP_PAGE);
+
+/* launch_sparse_mla_cache_append: writes a call's T new rows into a paged cache: row j of the n
+ * of request b goes to logical position L_b - n + j, L_b = seqused_kv[b] INCLUDING the new rows
+ * (the convention of the attention call that follows), through the request's block table.
+ * A position without a legal page is not written and is reported in the status block of
+ * `npu_workspace` (SPARSE_MLA_STATUS_BAD_PAGE, token, position).
+ *   new_rows      [T, 512]                    b16  read
+ *   cache         [BLOCKS, PAGE_ROWS, 1, 512] b16  write (rows not addressed keep their contents)
+ *   block_table   [B, PAGES]                  i32  read
+ *   cu_seqlens_q  [B + 1]                     i32  read
+ *   seqused_kv    [B]                         i32  read
+ * `npu_workspace`: workspace_size_sparse_mla bytes. PAGE_ROWS 128 (raw cache) or 64. */
+int launch_sparse_mla_cache_append(void* stream, void* arg_new_rows, void* arg_cache,
+                                   void* arg_block_table, void* arg_cu_seqlens_q, void* arg_seqused_kv,
+                                   void* npu_workspace, int64_t B, int64_t T, int64_t PAGES,
+                                   int64_t BLOCKS, int64_t PAGE_ROWS);
+
 /* Self-test of the bounded on-chip wait (no counterpart in the reference, whose synchronisation
  * is proven at compile time): one warp waits on a barrier nobody signals; after `limit_cycles`
  * SM clocks (<= 2^31) it gives up, writes SPARSE_MLA_STATUS_WAIT_EXPIRED to the status block of

@@ -282,6 +282,50 @@ def reference_fp32_from_data(data, policy, chunk=128):
 
 
 # --------------------------------------------------------------------------
+# the steps on either side of the operator (no reference implementation exists: the reference
+# leaves them to its caller, docs/operators/sparse-mla.md:8, 263-266; their contracts follow from
+# what the operator reads, docs/operators/sparse-mla.md:62-87). PARITY UNPINNED for these two:
+# there is no golden vector or reference output to pin them against, only the consistency checks
+# in tests/test_neighbours.py (the selection is what `resolve_rows` then accepts in full).
+# --------------------------------------------------------------------------
+
+def select_topk_indices(scores, data, policy):
+    """`cmp_sparse_indices` `[T, 1, TOPK]` from index scores `[T, SPAN]`.
+
+    Per token the candidates are compressed rows `[0, min(available, cutoff))` (what
+    `resolve_rows` accepts); the `min(TOPK, candidates)` highest scores win, ties going to the
+    lower index; winners in ascending order, then -1.
+    """
+    scores = np.asarray(scores, dtype=np.float32)
+    geometry = token_geometry(dict(data, ori_topk_length=np.zeros((scores.shape[0], 1), np.int32)), policy)
+    topk = int(policy["TOPK"])
+    out = np.full((scores.shape[0], 1, topk), -1, dtype=np.int32)
+    for token in range(scores.shape[0]):
+        candidates = int(min(geometry["available"][token], geometry["cutoff"][token], scores.shape[1]))
+        take = min(topk, candidates)
+        if take == 0:
+            continue
+        order = np.lexsort((np.arange(candidates), -scores[token, :candidates].astype(np.float64)))
+        out[token, 0, :take] = np.sort(order[:take]).astype(np.int32)
+    return out
+
+
+def append_rows(cache, new_rows, block_table, cu_seqlens_q, seqused_kv):
+    """A copy of the paged `cache` `[BLOCKS, PAGE_ROWS, 1, D]` with a call's `new_rows` `[T, D]`
+    written in: row j of the n of request b at logical position `seqused_kv[b] - n + j`."""
+    cache = np.array(cache, copy=True)
+    page_rows = cache.shape[1]
+    cu = np.asarray(cu_seqlens_q, dtype=np.int64)
+    for batch in range(len(cu) - 1):
+        count = int(cu[batch + 1] - cu[batch])
+        for offset in range(count):
+            position = int(seqused_kv[batch]) - count + offset
+            page = int(block_table[batch, position // page_rows])
+            cache[page, position % page_rows, 0] = new_rows[cu[batch] + offset]
+    return cache
+
+
+# --------------------------------------------------------------------------
 # input generators
 # --------------------------------------------------------------------------
 
