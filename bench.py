@@ -49,7 +49,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # sources whose hash is recorded with them: a line measured with other sources says so.
 MEASURED_TRAFFIC = {
     "prefill": {"bytes_per_token": 1078.24e6 / 8192, "profile": "profiles/attention_kernel_prefill_q8k_ctx32k.md"},
-    "decode": {"bytes_per_token": 59.10e6 / 96, "profile": "profiles/attention_kernel_decode_b16_q6_ctx128k.md"},
+    # decode: one-pass captures of the full-size calls (768 / 384 / 96 query tokens per launch)
+    "decode": {"bytes_per_token": 503.43e6 / 768, "profile": "profiles/attention_kernel_decode_dram_traffic.md",
+               "per_launch": {768: 503.43e6, 384: 245.31e6, 96: 58.76e6}},
     "source_sha256": "31d15cff6eaacb16b1cec95b37bbd576441bc836a7d5742e7c3d944669904dde",
 }
 EXTRA_WORKLOADS = ("prefill_q32k_ctx32k", "decode_b64_q6_ctx128k", "decode_b128_q6_ctx128k")
@@ -245,8 +247,10 @@ def roofline_of(config, work, ms, world, source_sha):
         record = {"bound": "tensor", "achieved": achieved, "peak": peak["bf16_tflops"], "unit": "TFLOP/s"}
     record["frac"] = record["achieved"] / record["peak"]
     traffic = MEASURED_TRAFFIC[regime]
-    record["traffic"] = traffic["bytes_per_token"] * work["tokens"] / world
-    record["traffic_source"] = (f"ncu capture summarised in {traffic['profile']}, scaled by tokens; captured with "
+    measured = traffic.get("per_launch", {}).get(work["tokens"]) if world == 1 else None
+    record["traffic"] = measured if measured else traffic["bytes_per_token"] * work["tokens"] / world
+    record["traffic_source"] = (f"ncu capture summarised in {traffic['profile']}, "
+                                f"{'of this very call' if measured else 'scaled by tokens'}; captured with "
                                 f"kernel sources {MEASURED_TRAFFIC['source_sha256'][:12]}"
                                 + ("" if MEASURED_TRAFFIC["source_sha256"] == source_sha else
                                    f" (this run: {source_sha[:12]}, so the figure may be stale)"))
