@@ -98,6 +98,39 @@ def test_gpu_selection_matches_the_oracle_bit_for_bit(ratio, seed):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("max_seq,ratio", [(131072, 2), (32768, 2), (131072, 1), (262144, 2)])
+def test_gpu_selection_over_long_rows(max_seq, ratio):
+    """Decode-sized rows: up to 65536 scores are selected from one read (upper key halves kept in
+    shared memory), longer rows by the streaming kernel. Continuous scores, heavy ties, one row of
+    nothing but ties (more of them than the kernel's tie list holds), one of negative values."""
+    import torch
+
+    from ascendflow_b200 import neighbours
+
+    rng = np.random.default_rng(max_seq // 1024 + ratio)
+    lens = [2, 1, 3, 2]
+    span = max_seq // ratio
+    policy = O.make_policy(len(lens), sum(lens), ratio=ratio, max_seq=max_seq, blocks=8)
+    lengths = np.array([max_seq, max_seq - 5, 4100, 700], dtype=np.int32)   # long, long, short, under TopK
+    data = {
+        "cu_seqlens_q": np.concatenate([[0], np.cumsum(lens)]).astype(np.int32),
+        "seqused_ori_kv": lengths,
+        "seqused_cmp_kv": (lengths // ratio).astype(np.int32),
+        "cmp_residual_kv": (lengths % ratio).astype(np.int32),
+    }
+    scores = rng.normal(size=(sum(lens), span)).astype(np.float32)
+    scores[1] = np.round(scores[1] * 4) / 4           # a few dozen distinct values: long runs of ties
+    scores[2] = -3.5                                  # nothing but ties
+    scores[3] = -np.abs(scores[3])                    # negative keys only
+    scores[4, ::7] = np.float32(2.0)                  # a plateau that the threshold falls into
+    expected = O.select_topk_indices(scores, data, policy)
+    device = {k: torch.from_numpy(v).cuda() for k, v in data.items()}
+    actual = neighbours.topk_indices(torch.from_numpy(scores).cuda(), device["cu_seqlens_q"], device["seqused_cmp_kv"],
+                                     device["cmp_residual_kv"], ratio=ratio)
+    assert np.array_equal(actual.cpu().numpy(), expected)
+
+
+@pytest.mark.gpu
 def test_gpu_selection_feeds_the_attention_call():
     """Scores -> indices on the device -> attention, against the oracle fed with the oracle's selection."""
     import torch
