@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(kSelectThreads) topk_select_kernel(const Selec
   __shared__ unsigned prefix_key, wanted;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int kStep = kSelectThreads * 4;
+  constexpr int kInFlight = 2;  // 16-byte loads in flight per thread in the counting passes (four: slower)
   for (int token = blockIdx.x; token < p.tokens; token += gridDim.x) {
     const int candidates = int(min((int64_t)visible_compressed_rows(p, token), p.span));
     const int take = min(kTopK, candidates);
@@ -96,16 +97,18 @@ __global__ void __launch_bounds__(kSelectThreads) topk_select_kernel(const Selec
       const unsigned mask = digit == 3 ? 0u : (0xffffffffu << (shift + 8));
       // Lanes that fall into the same bin (most of them, for the exponent digit) add once,
       // through their lowest lane.
-      for (int first = 0; first < candidates; first += 2 * kStep) {
-        uint32_t key[2][4];
-        bool valid[2][4];
-        load_keys(row, first + threadIdx.x * 4, candidates, key[0], valid[0]);
-        load_keys(row, first + kStep + threadIdx.x * 4, candidates, key[1], valid[1]);
+      for (int first = 0; first < candidates; first += kInFlight * kStep) {
+        uint32_t key[kInFlight][4];
+        bool valid[kInFlight][4];
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+        for (int h = 0; h < kInFlight; ++h) load_keys(row, first + h * kStep + threadIdx.x * 4, candidates, key[h], valid[h]);
+#pragma unroll
+        for (int h = 0; h < kInFlight; ++h)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const bool counted = valid[h][e] && (key[h][e] & mask) == prefix;
+            // from the second digit on, most warps hold no entry with the prefix: nothing to vote on
+            if (__ballot_sync(0xffffffffu, counted) == 0u) continue;
             const unsigned bin = counted ? (key[h][e] >> shift) & 255u : 256u;
             const unsigned peers = __match_any_sync(0xffffffffu, bin);
             if (counted && lane == __ffs(peers) - 1) atomicAdd(&histogram[warp][bin], unsigned(__popc(peers)));
