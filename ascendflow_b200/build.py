@@ -68,9 +68,23 @@ def is_current():
     return LIBRARY.exists() and STAMP.exists() and STAMP.read_text() == _identity()
 
 
+ATTENTION_KERNEL_SOURCES = ("sparse_mla_common.cuh", "tcgen05_ptx.cuh", "sparse_mla_tcgen05.cuh")
+
+
+def attention_kernel_identity():
+    """Hash of the files the tcgen05 attention kernel is compiled from (and of the flags): what a
+    profile of that kernel is a profile of, whatever else in the library changes."""
+    digest = hashlib.sha256(" ".join(FLAGS).encode())
+    for name in ATTENTION_KERNEL_SOURCES:
+        digest.update(name.encode())
+        digest.update((PACKAGE / "csrc" / name).read_bytes())
+    return digest.hexdigest()
+
+
 def identity():
     """What the result records say about the binary: compiler flags and a hash of the sources."""
-    return {"flags": " ".join(FLAGS), "source_sha256": _identity(), "library": LIBRARY.name,
+    return {"flags": " ".join(FLAGS), "source_sha256": _identity(),
+            "attention_kernel_sha256": attention_kernel_identity(), "library": LIBRARY.name,
             "library_is_current": is_current()}
 
 

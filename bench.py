@@ -52,7 +52,7 @@ MEASURED_TRAFFIC = {
     # decode: one-pass captures of the full-size calls (768 / 384 / 96 query tokens per launch)
     "decode": {"bytes_per_token": 503.43e6 / 768, "profile": "profiles/attention_kernel_decode_dram_traffic.md",
                "per_launch": {768: 503.43e6, 384: 245.31e6, 96: 58.76e6}},
-    "source_sha256": "31d15cff6eaacb16b1cec95b37bbd576441bc836a7d5742e7c3d944669904dde",
+    "attention_kernel_sha256": "cf219b2916c73021fcc7b13f2ccb3d2f10457042d5341a70c42cd3ad2728e22b",
 }
 EXTRA_WORKLOADS = ("prefill_q32k_ctx32k", "decode_b64_q6_ctx128k", "decode_b128_q6_ctx128k")
 CONFIG_KEYS = {"heads": 64, "features": 512, "topk": 512, "window": 128, "ratio": 2, "values": "N(0,1)",
@@ -251,8 +251,8 @@ def roofline_of(config, work, ms, world, source_sha):
     record["traffic"] = measured if measured else traffic["bytes_per_token"] * work["tokens"] / world
     record["traffic_source"] = (f"ncu capture summarised in {traffic['profile']}, "
                                 f"{'of this very call' if measured else 'scaled by tokens'}; captured with "
-                                f"kernel sources {MEASURED_TRAFFIC['source_sha256'][:12]}"
-                                + ("" if MEASURED_TRAFFIC["source_sha256"] == source_sha else
+                                f"kernel sources {MEASURED_TRAFFIC['attention_kernel_sha256'][:12]}"
+                                + ("" if MEASURED_TRAFFIC["attention_kernel_sha256"] == source_sha else
                                    f" (this run: {source_sha[:12]}, so the figure may be stale)"))
     record["peak_source"] = f"{source} (burst figure: each launch is timed alone between L2 evictions)"
     record["per_gpu"] = "achieved is per GPU: the whole call's work / GPUs / slowest rank's time"
@@ -472,7 +472,7 @@ def run_b200(args, config):
         work = call.work
         record = {
             "ms_per_step": ms, "value": work["flops"] / (ms * 1e-3) / 1e12, "unit": UNIT,
-            "roofline": roofline_of(workload, work, ms, world, identity["source_sha256"]),
+            "roofline": roofline_of(workload, work, ms, world, identity["attention_kernel_sha256"]),
             "clocks": dict(clocks.summary(), region=f"timed region ({timed_seconds:.2f} s) plus {held} identical "
                                                     "untimed launches so that the 100 ms sampler sees the load"),
             "config": {"workload": name, **workload, **CONFIG_KEYS,
